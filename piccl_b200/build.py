@@ -76,7 +76,7 @@ def _run(cmd: list[str], verbose: bool) -> None:
         print(" ".join(shlex.quote(c) for c in cmd), flush=True)
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
-        raise RuntimeError(f"command failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+        raise RuntimeError(f"command failed: {' '.join(cmd)}\n{r.stdout[-3000:]}\n{r.stderr[-3000:]}")
     if verbose and (r.stdout.strip() or r.stderr.strip()):
         print(r.stdout, r.stderr, flush=True)
 

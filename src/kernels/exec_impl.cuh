@@ -1,0 +1,323 @@
+// The fused collective executor: ONE kernel runs a whole collective.  Each CTA
+// owns a fixed slice of every action; for each FIFO segment it walks the
+// action program, and every action is a single pass
+//     wait (bounded) -> load local + incoming slots -> reduce in registers ->
+//     store local + peers' slots -> publish counters
+// so reduction (reference: src/kernels/reduce_kernel.cu, one launch per step)
+// and block placement (reference: src/kernels/permutation_kernel.cu) never
+// exist as separate passes, and no ncclSend/ncclRecv is issued.
+//
+// Peer traffic is plain 16-byte stores into the peer's mapped heap (NVLink /
+// NVSwitch P2P); ordering is fence.acq_rel.sys + st.release.sys on the
+// producer and ld.acquire.sys on the consumer.  Every wait has a time limit;
+// on expiry the CTA records where it gave up, raises the abort flag that all
+// other waits poll, and the kernel returns.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include "exec.cuh"
+#include "../include/piccl_slice.h"
+
+namespace piccl {
+
+// ---------------------------------------------------------------- memory primitives
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void fence_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// FIFO payload written by another GPU: read past L1.
+__device__ __forceinline__ uint4 ld_slot(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_local(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ void st_vec(void* p, const uint4& v) { *reinterpret_cast<uint4*>(p) = v; }
+
+// ---------------------------------------------------------------- element-wise maths
+template <int OP, typename A> __device__ __forceinline__ A red(A x, A y) {
+  if (OP == 0) return x + y;
+  if (OP == 1) return x * y;
+  if (OP == 2) return x > y ? x : y;
+  return x < y ? x : y;
+}
+
+template <typename T> struct AccOf { typedef T type; };
+template <> struct AccOf<__half> { typedef float type; };
+template <> struct AccOf<__nv_bfloat16> { typedef float type; };
+
+template <typename T> struct Cvt {
+  typedef typename AccOf<T>::type A;
+  static __device__ __forceinline__ A up(T v) { return (A)v; }
+  static __device__ __forceinline__ T down(A v) { return (T)v; }
+};
+template <> struct Cvt<__half> {
+  static __device__ __forceinline__ float up(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half down(float v) { return __float2half_rn(v); }
+};
+template <> struct Cvt<__nv_bfloat16> {
+  static __device__ __forceinline__ float up(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 down(float v) { return __float2bfloat16_rn(v); }
+};
+
+template <typename T> struct Pack {
+  static constexpr int N = 16 / sizeof(T);
+  typedef typename AccOf<T>::type A;
+  union U { uint4 v; T t[N]; };
+  static __device__ __forceinline__ void up(const uint4& v, A (&a)[N]) {
+    U u; u.v = v;
+#pragma unroll
+    for (int i = 0; i < N; i++) a[i] = Cvt<T>::up(u.t[i]);
+  }
+  static __device__ __forceinline__ uint4 down(const A (&a)[N]) {
+    U u;
+#pragma unroll
+    for (int i = 0; i < N; i++) u.t[i] = Cvt<T>::down(a[i]);
+    return u.v;
+  }
+};
+
+template <typename A> __device__ __forceinline__ A scale_val(A v, float s) { return v; }
+template <> __device__ __forceinline__ float scale_val<float>(float v, float s) { return v * s; }
+template <> __device__ __forceinline__ double scale_val<double>(double v, float s) { return v * (double)s; }
+
+// ---------------------------------------------------------------- bounded wait
+struct WaitCtx { RankCtx* ctx; unsigned long long timeout_ns; int cta, action, segment; };
+
+// Returns false if the wait was given up (time limit or abort raised elsewhere).
+static __device__ __noinline__ bool wait_counter(const unsigned long long* flag, unsigned long long want, const WaitCtx& w, int code, int peer) {
+  unsigned long long t0 = 0, have = 0;
+  for (unsigned spins = 1;; spins++) {
+    have = ld_acquire_sys(flag);
+    if (have >= want) return true;
+    if ((spins & 31u) == 0) {
+      if (*(volatile int*)w.ctx->abort_flag) return false;
+      unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > w.timeout_ns) break;
+    }
+  }
+  // first CTA to give up records where; everybody else just leaves
+  if (atomicCAS(w.ctx->abort_flag, 0, 1) == 0) {
+    piccl_status_t* s = w.ctx->status;
+    s->code = code; s->rank = w.ctx->rank; s->cta = w.cta; s->action = w.action; s->peer = peer; s->segment = w.segment;
+    s->want = want; s->have = have;
+    __threadfence_system();
+    s->aborted = 1;
+    __threadfence_system();
+  }
+  return false;
+}
+
+// ---------------------------------------------------------------- data movement
+// value = reduce(src[0..nsrc)) -> dst[0..ndst); `local_src` (index or -1) is the
+// user-buffer operand (plain loads, optional scaling); the other sources are FIFO slots.
+template <typename T, int OP, int U>
+__device__ __forceinline__ void reduce_copy_vec(int nsrc, const char* const* src, int local_src, int ndst, char* const* dst,
+                                                long long npack, bool do_scale, float scale) {
+  typedef typename AccOf<T>::type A;
+  constexpr int N = Pack<T>::N;
+  const int nt = blockDim.x;
+  for (long long base = threadIdx.x; base < npack; base += (long long)nt * U) {
+    if (nsrc == 1 && !do_scale) {           // pure copy: no conversion
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        long long i = base + (long long)u * nt;
+        if (i < npack) v[u] = (local_src == 0) ? ld_local(src[0] + i * 16) : ld_slot(src[0] + i * 16);
+      }
+      for (int d = 0; d < ndst; d++) {
+#pragma unroll
+        for (int u = 0; u < U; u++) { long long i = base + (long long)u * nt; if (i < npack) st_vec(dst[d] + i * 16, v[u]); }
+      }
+      continue;
+    }
+    A acc[U][N];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      long long i = base + (long long)u * nt;
+      if (i < npack) {
+        uint4 v = (local_src == 0) ? ld_local(src[0] + i * 16) : ld_slot(src[0] + i * 16);
+        Pack<T>::up(v, acc[u]);
+        if (do_scale && local_src == 0) {
+#pragma unroll
+          for (int e = 0; e < N; e++) acc[u][e] = scale_val<A>(acc[u][e], scale);
+        }
+      }
+    }
+    for (int s = 1; s < nsrc; s++) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        long long i = base + (long long)u * nt;
+        if (i < npack) v[u] = (local_src == s) ? ld_local(src[s] + i * 16) : ld_slot(src[s] + i * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        long long i = base + (long long)u * nt;
+        if (i < npack) {
+          A x[N]; Pack<T>::up(v[u], x);
+#pragma unroll
+          for (int e = 0; e < N; e++) {
+            A xv = (do_scale && local_src == s) ? scale_val<A>(x[e], scale) : x[e];
+            acc[u][e] = red<OP, A>(acc[u][e], xv);
+          }
+        }
+      }
+    }
+    for (int d = 0; d < ndst; d++) {
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        long long i = base + (long long)u * nt;
+        if (i < npack) st_vec(dst[d] + i * 16, Pack<T>::down(acc[u]));
+      }
+    }
+  }
+}
+
+// Element-wise path: unaligned user buffers and the last, partial pack of an action.
+template <typename T, int OP>
+__device__ __forceinline__ void reduce_copy_elem(int nsrc, const char* const* src, int local_src, int ndst, char* const* dst,
+                                                 long long first, long long nelem, bool do_scale, float scale) {
+  typedef typename AccOf<T>::type A;
+  for (long long i = first + threadIdx.x; i < nelem; i += blockDim.x) {
+    A acc = A();
+    for (int s = 0; s < nsrc; s++) {
+      const T* p = reinterpret_cast<const T*>(src[s]) + i;
+      T raw = (local_src == s) ? *p : *reinterpret_cast<const volatile T*>(p);
+      A x = Cvt<T>::up(raw);
+      if (do_scale && local_src == s) x = scale_val<A>(x, scale);
+      acc = (s == 0) ? x : red<OP, A>(acc, x);
+    }
+    T o = Cvt<T>::down(acc);
+    for (int d = 0; d < ndst; d++) reinterpret_cast<T*>(dst[d])[i] = o;
+  }
+}
+
+// ---------------------------------------------------------------- the kernel
+template <typename T, int OP>
+__global__ void __launch_bounds__(kMaxBlock, 1) exec_kernel(const KernelArgs ka) {
+  const int vr = blockIdx.x / ka.n_cta, cta = blockIdx.x % ka.n_cta;
+  const LaunchRank& L = ka.r[vr];
+  RankCtx* __restrict__ ctx = L.ctx;
+  const int tid = threadIdx.x;
+  const int rank = ctx->rank, nranks = ctx->nranks, max_cta = ctx->max_cta, nslot = ctx->nslot;
+  const long long slot_bytes = ctx->slot_bytes;
+  char* const my_heap = ctx->heap[rank];
+  constexpr int esz = (int)sizeof(T);
+
+  __shared__ int s_send_slot[kMaxRanks], s_recv_slot[kMaxRanks];
+  __shared__ int s_fail, s_maxseg;
+
+  // thread p (< nranks) owns the two counters of the connections with peer p
+  unsigned long long my_sent = 0, my_rcvd = 0;
+  if (tid < nranks) { my_sent = ctx->sent[tid * max_cta + cta]; my_rcvd = ctx->rcvd[tid * max_cta + cta]; }
+  if (tid == 0) { s_fail = 0; s_maxseg = 0; }
+  __syncthreads();
+  {
+    int m = 0;
+    for (int ai = tid; ai < L.n_actions; ai += blockDim.x) m = max(m, slice_of(L.actions[ai].count, esz, cta, ka.n_cta, slot_bytes).nseg);
+    if (m) atomicMax(&s_maxseg, m);
+  }
+  __syncthreads();
+  const int maxseg = s_maxseg;
+  WaitCtx w; w.ctx = ctx; w.timeout_ns = ka.timeout_ns; w.cta = cta;
+  bool failed = false;
+
+  for (int seg = 0; seg < maxseg && !failed; seg++) {
+    for (int ai = 0; ai < L.n_actions; ai++) {
+      const Action ac = L.actions[ai];
+      const Slice sl = slice_of(ac.count, esz, cta, ka.n_cta, slot_bytes);
+      if (seg >= sl.nseg) continue;
+      const long long lo = sl.lo + (long long)seg * sl.seg_elems;
+      const long long hi = (lo + sl.seg_elems < sl.hi) ? lo + sl.seg_elems : sl.hi;
+      const long long len = hi - lo;
+
+      // ---- wait: credit on every send connection, data on every receive connection
+      if (tid < nranks) {
+        bool ok = true;
+        w.action = ai; w.segment = seg;
+        for (int j = 0; j < ac.n_send; j++) if (ac.send_peer[j] == tid) {
+          s_send_slot[tid] = (int)(my_sent % (unsigned)nslot);
+          if (my_sent + 1 > (unsigned long long)nslot)
+            ok = wait_counter(reinterpret_cast<const unsigned long long*>(my_heap + ctx->head_off + (long long)(tid * max_cta + cta) * kFlagStride),
+                              my_sent + 1 - nslot, w, 1, tid);
+        }
+        for (int j = 0; j < ac.n_recv && ok; j++) if (ac.recv_peer[j] == tid) {
+          s_recv_slot[tid] = (int)(my_rcvd % (unsigned)nslot);
+          ok = wait_counter(reinterpret_cast<const unsigned long long*>(my_heap + ctx->tail_off + (long long)(tid * max_cta + cta) * kFlagStride),
+                            my_rcvd + 1, w, 2, tid);
+        }
+        if (!ok) s_fail = 1;
+      }
+      __syncthreads();
+      if (s_fail) { failed = true; break; }
+
+      // ---- operands, in rank order: receive peers below me, my own buffer, receive peers above me
+      const char* src[kMaxActionPeers + 1]; char* dst[kMaxActionPeers + 1];
+      int nsrc = 0, ndst = 0, local_src = -1;
+      bool aligned = true;
+      const bool has_src = ac.src_buf != BUF_NONE;
+      for (int j = 0; j <= ac.n_recv; j++) {
+        if (j == ac.self_pos && has_src) {
+          const char* base = ac.src_buf == BUF_IN ? (const char*)L.in : ac.src_buf == BUF_OUT ? (const char*)L.out : my_heap + ctx->scratch_off;
+          src[nsrc] = base + (ac.src_off + lo) * esz;
+          aligned &= ((reinterpret_cast<uintptr_t>(src[nsrc]) & 15) == 0);
+          local_src = nsrc++;
+        }
+        if (j < ac.n_recv) {
+          const int p = ac.recv_peer[j];
+          src[nsrc++] = my_heap + ctx->fifo_off + ((long long)(p * max_cta + cta) * nslot + s_recv_slot[p]) * slot_bytes;
+        }
+      }
+      if (ac.dst_buf != BUF_NONE) {
+        char* base = ac.dst_buf == BUF_OUT ? (char*)L.out : my_heap + ctx->scratch_off;
+        dst[ndst] = base + (ac.dst_off + lo) * esz;
+        aligned &= ((reinterpret_cast<uintptr_t>(dst[ndst]) & 15) == 0);
+        ndst++;
+      }
+      for (int j = 0; j < ac.n_send; j++) {
+        const int p = ac.send_peer[j];
+        dst[ndst++] = ctx->heap[p] + ctx->fifo_off + ((long long)(rank * max_cta + cta) * nslot + s_send_slot[p]) * slot_bytes;
+      }
+      const bool do_scale = ka.avg && (ac.flags & ACT_SCALE_SRC) && local_src >= 0;
+
+      // ---- one pass over the segment
+      constexpr int N = Pack<T>::N;
+      long long nfull = aligned ? len / N : 0;
+      if (nfull) reduce_copy_vec<T, OP, 4>(nsrc, src, local_src, ndst, dst, nfull, do_scale, ka.scale);
+      if (nfull * N < len) reduce_copy_elem<T, OP>(nsrc, src, local_src, ndst, dst, nfull * N, len, do_scale, ka.scale);
+      __syncthreads();
+
+      // ---- publish: the data to the consumers, the freed slot to the producers
+      if (tid < nranks) {
+        for (int j = 0; j < ac.n_send; j++) if (ac.send_peer[j] == tid) {
+          my_sent++;
+          st_release_sys(reinterpret_cast<unsigned long long*>(ctx->heap[tid] + ctx->tail_off + (long long)(rank * max_cta + cta) * kFlagStride), my_sent);
+        }
+        for (int j = 0; j < ac.n_recv; j++) if (ac.recv_peer[j] == tid) {
+          my_rcvd++;
+          st_release_sys(reinterpret_cast<unsigned long long*>(ctx->heap[tid] + ctx->head_off + (long long)(rank * max_cta + cta) * kFlagStride), my_rcvd);
+        }
+      }
+    }
+  }
+  if (tid < nranks) { ctx->sent[tid * max_cta + cta] = my_sent; ctx->rcvd[tid * max_cta + cta] = my_rcvd; }
+}
+
+#define PICCL_INSTANTIATE_EXEC(T, DT)                                                              \
+  namespace piccl {                                                                                \
+  ExecKernelFn exec_table_##DT[4] = {exec_kernel<T, 0>, exec_kernel<T, 1>, exec_kernel<T, 2>, exec_kernel<T, 3>}; \
+  }
+
+}  // namespace piccl

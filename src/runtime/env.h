@@ -1,0 +1,32 @@
+// Environment configuration, read once per process.
+//
+// Same variables, values and defaults as the reference
+// (README.md:46-68; parsing src/piccl.c:224-334): PICCL_<COLL>_ALGO in
+// {RING,K_RING,RD,RM,PRD,PRM} (anything else or unset: real NCCL), PICCL_<COLL>_K
+// (default -1), PICCL_BLOCK_SIZE (1024), PICCL_MAX_GRID_SIZE (1024),
+// PICCL_MIN_GRID_SIZE (1).  Additions that do not change those semantics: the
+// value AUTO, PICCL_TIMEOUT_MS, PICCL_SCRATCH_MB, PICCL_SLOT_KB, PICCL_NSLOT,
+// PICCL_MAX_CTA, PICCL_LOG, PICCL_TRACE, PICCL_FAULT, PICCL_TUNE_FILE, PICCL_DEBUG.
+#pragma once
+#include <string>
+#include "../include/piccl_sched.h"
+
+namespace piccl {
+
+struct Env {
+  Algo algo[COLL_COUNT];
+  int k[COLL_COUNT];
+  int block_size, max_grid, min_grid;          // reference knobs (now size the fused executor)
+  bool block_size_set, max_grid_set, min_grid_set;
+  int timeout_ms, scratch_mb, slot_kb, nslot, max_cta;
+  int log_level, debug;
+  std::string trace_file, tune_file;
+  // host-side fault injection: rank:call:{skip_call|delay_ms=N}
+  int fault_rank, fault_call, fault_delay_ms; bool fault_skip;
+};
+
+const Env& env();
+void env_reload();                 // tests only
+void log_msg(int level, const char* fmt, ...);
+
+}  // namespace piccl

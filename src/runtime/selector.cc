@@ -1,0 +1,57 @@
+// Algorithm / radix selection for requests that name no algorithm (AUTO).
+// PICCL_TUNE_FILE points to the table written by tools/selector (CSV:
+// collective,nranks,max_bytes,algorithm,k — first row whose max_bytes is not
+// below the message wins).  Without a table the built-in rule is used: one
+// exchange step with every rank (PRM, k = n) while the message is latency
+// bound, the bandwidth-optimal ring above that.  The reference has no
+// selector: the user picks through the environment (src/piccl.c:257-285).
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include "comm.h"
+
+namespace piccl {
+
+static std::vector<TuneRow> g_rows;
+static std::once_flag g_once;
+
+static void load_table() {
+  const std::string& path = env().tune_file;
+  if (path.empty()) return;
+  FILE* f = fopen(path.c_str(), "r");
+  if (!f) { log_msg(1, "tuning table %s not readable", path.c_str()); return; }
+  char line[256];
+  while (fgets(line, sizeof line, f)) {
+    char coll[32], algo[32]; int n, k; long long mb;
+    if (line[0] == '#' || sscanf(line, "%31[^,],%d,%lld,%31[^,],%d", coll, &n, &mb, algo, &k) != 5) continue;
+    int ci = -1;
+    for (int c = 0; c < COLL_COUNT; c++) if (!strcmp(coll, coll_name((Coll)c))) ci = c;
+    Algo a = algo_from_string(algo);
+    if (ci < 0 || a == ALGO_DEFAULT_NCCL || a == ALGO_AUTO) continue;
+    g_rows.push_back(TuneRow{ci, n, mb, a, k});
+  }
+  fclose(f);
+  log_msg(1, "tuning table %s: %zu rows", path.c_str(), g_rows.size());
+}
+
+Algo select_algo_n(int n, Coll coll, size_t bytes, int* k) {
+  std::call_once(g_once, load_table);
+  for (auto& r : g_rows)
+    if (r.coll == coll && r.nranks == n && (long long)bytes <= r.max_bytes) { if (k) *k = r.k; return r.algo; }
+  int kk = n < 8 ? n : 8;
+  switch (coll) {
+    case COLL_ALLREDUCE:
+      if (bytes <= (size_t)256 << 10) { if (k) *k = kk; return ALGO_PRM; }
+      return ALGO_RING;
+    case COLL_ALLGATHER: case COLL_REDUCE_SCATTER:
+      if (bytes <= (size_t)1 << 20) { if (k) *k = kk; return ALGO_PRM; }
+      return ALGO_RING;
+    default:
+      if (bytes <= (size_t)1 << 20) { if (k) *k = kk; return ALGO_PRM; }
+      return ALGO_RING;
+  }
+}
+
+Algo select_algo(piccl_comm* c, Coll coll, size_t bytes, int* k) { return select_algo_n(c->nranks, coll, bytes, k); }
+
+}  // namespace piccl
