@@ -47,7 +47,7 @@ def _ref_reduce(xs, op):
 
 
 def _tol(dtype, n):
-    return {torch.float32: 1e-5 * n, torch.bfloat16: 2e-2, torch.float16: 2e-3}.get(dtype, 0.0)
+    return {torch.float32: 1e-5 * n, torch.float64: 1e-5 * n, torch.bfloat16: 2e-2, torch.float16: 2e-3}.get(dtype, 0.0)
 
 
 def _check_ok(g):
