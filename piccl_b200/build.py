@@ -54,8 +54,8 @@ def targets() -> dict[str, dict]:
             "link": [],
         },
         "coll_bench": {
-            "src": [ROOT / "bench" / "coll_bench.cc"],
-            "link": ["-cudart", "static", "-ldl", "-lpthread", "-lrt"],
+            "src": [ROOT / "benchmarks" / "coll_bench.cc"],
+            "link": ["-cudart", "static", "-ldl", "-lpthread", "-lrt", "-L/usr/lib/x86_64-linux-gnu", "-lnccl"],
         },
     }
 

@@ -1,0 +1,42 @@
+"""Front end of the tcgen05 GEMM (src/ops/gemm_sm100.cu)."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from .. import _native as N
+from . import _bump
+
+_checked = None
+
+
+def available() -> bool:
+    global _checked
+    if _checked is None:
+        try:
+            lib = N.ops_lib()
+            _checked = hasattr(lib, "piccl_ops_gemm_bf16_nt") and torch.cuda.is_available() and torch.cuda.get_device_capability()[0] == 10
+        except Exception:
+            _checked = False
+    return _checked
+
+
+def supports(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    M, K = x.shape
+    Nn = w.shape[0]
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
+            and out.is_contiguous() and K % 64 == 0 and Nn % 128 == 0 and M % 128 == 0 and K >= 64)
+
+
+def gemm_nt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None, gelu: bool = False) -> torch.Tensor:
+    """out[M, N] = act(x[M, K] @ w[N, K]^T + bias)"""
+    M, K = x.shape
+    Nn = w.shape[0]
+    rc = N.ops_lib().piccl_ops_gemm_bf16_nt(C.c_void_p(x.data_ptr()), C.c_void_p(w.data_ptr()), C.c_void_p(out.data_ptr()),
+                                            C.c_void_p(bias.data_ptr() if bias is not None else 0), M, Nn, K, int(gelu),
+                                            C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    if rc != 0:
+        raise RuntimeError(f"piccl_ops_gemm_bf16_nt failed (code {rc}) for M={M} N={Nn} K={K}")
+    _bump()
+    return out

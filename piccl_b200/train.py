@@ -1,0 +1,65 @@
+"""Public training entry point: data-parallel GPT-2 training steps.
+
+    trainer = DataParallelTrainer(GPT2Config.medium())      # one process per GPU
+    loss = trainer.step(tokens_cpu, targets_cpu)            # pinned host tensors in, python float out
+
+`step` copies the batch from (pinned) host memory, runs forward, backward with
+bucketed gradient averaging overlapped on a second stream, the fused AdamW
+update, and reads the loss back.  `step_device` is the same without the two host
+transfers.
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+
+from . import ops
+from .models.gpt2 import GPT2, GPT2Config
+from .parallel.comm import Communicator
+from .parallel.ddp import GradAverager
+
+
+class DataParallelTrainer:
+    def __init__(self, cfg: GPT2Config, comm: Optional[Communicator] = None, lr: float = 3e-4, weight_decay: float = 0.1,
+                 bucket_bytes: int = 25 * 1024 * 1024, algo: Optional[str] = None, k: int = -1, seed: int = 0):
+        self.cfg = cfg
+        self.model = GPT2(cfg, device=torch.device("cuda", torch.cuda.current_device()), seed=seed)
+        self.comm = comm
+        algo = algo or os.environ.get("PICCL_ALLREDUCE_ALGO", "AUTO")
+        if k < 0:
+            k = int(os.environ.get("PICCL_ALLREDUCE_K", "-1"))
+        self.averager = GradAverager(self.model.flat_g, comm, bucket_bytes, algo, k)
+        self.lr, self.weight_decay = lr, weight_decay
+        self._idx = None
+        self._tgt = None
+        self._loss_host = torch.empty(1, dtype=torch.float32).pin_memory()
+        if comm is not None and comm.nranks > 1:
+            # identical parameters everywhere: rank 0's initial values (all ranks seed alike; this makes it explicit)
+            comm.broadcast(self.model.flat_p, root=0, algo="RING")
+            self.model.master.copy_(self.model.flat_p.float())
+
+    def step_device(self, idx: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        self.averager.begin_step()
+        loss = self.model.forward_backward(idx, targets, on_grads_ready=self.averager.ready)
+        self.averager.finish()
+        self.model.optimizer_step(lr=self.lr, weight_decay=self.weight_decay)
+        return loss
+
+    def step(self, idx_host: torch.Tensor, targets_host: torch.Tensor) -> float:
+        if self._idx is None or self._idx.shape != idx_host.shape:
+            self._idx = torch.empty(idx_host.shape, dtype=torch.int64, device="cuda")
+            self._tgt = torch.empty(targets_host.shape, dtype=torch.int64, device="cuda")
+        self._idx.copy_(idx_host, non_blocking=True)
+        self._tgt.copy_(targets_host, non_blocking=True)
+        loss = self.step_device(self._idx, self._tgt)
+        self._loss_host.copy_(loss.reshape(1), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return float(self._loss_host[0])
+
+    def kernel_launches(self) -> int:
+        n = ops.launch_count()
+        if self.comm is not None:
+            n += int(self.comm.stats().launches)
+        return n
