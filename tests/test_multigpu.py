@@ -21,7 +21,8 @@ def _ranks():
 
 def _run(case, extra_env=None, nproc=None, timeout=600):
     n = nproc or _ranks()
-    if n < 2:
+    have = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    if n < 2 or have < n:
         pytest.skip("needs at least two GPUs")
     env = dict(os.environ)
     env.update({"NCCL_NVLS_ENABLE": "0", "MASTER_ADDR": "127.0.0.1"})
