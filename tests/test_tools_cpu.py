@@ -1,0 +1,154 @@
+"""Offline tool chain: schedule generator CLI, LogGP simulator (classical model and the mode that
+reproduces the simulator shipped with the reference), parameter fitter, selector."""
+import subprocess
+import sys
+import xml.etree.ElementTree as ET
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+from tools.loggp_param import get_loggp_param as fitter  # noqa: E402
+from tools.loggp_sim import sim as S  # noqa: E402
+from tools.schedule_generator import main as gen  # noqa: E402
+
+
+@pytest.fixture()
+def world(tmp_path):
+    """Two parameter files with round numbers and two topologies (2 or 4 groups of 4 nodes, one NIC per group)."""
+    (tmp_path / "intra.csv").write_text("s,L,o_s,o_r,g,G\n1,10,5,6,8,1\n2,10,5,6,8,1\n")
+    (tmp_path / "inter.csv").write_text("s,L,o_s,o_r,g,G\n1,100,5,6,80,10\n2,100,5,6,80,10\n")
+
+    def topo(groups):
+        body = ""
+        for g in range(groups):
+            nodes = "".join(f'<node id="{4 * g + i}"/>' for i in range(4))
+            body += f'<group level="0" id="{g}" ports="1" param_file="{tmp_path / "intra.csv"}">{nodes}</group>'
+        p = tmp_path / f"topo{groups}.xml"
+        p.write_text(f'<topo num_nodes="{4 * groups}" num_levels="2"><group level="1" id="0" param_file="{tmp_path / "inter.csv"}">{body}</group></topo>')
+        return p
+
+    def sched(transfers, name="s"):
+        p = tmp_path / f"{name}.xml"
+        rows = "\n".join(f'  <transfer id="{i}" size="{sz}" src="{a}" dst="{b}" deps="{d}"/>' for i, (sz, a, b, d) in enumerate(transfers))
+        p.write_text(f'<collective name="t" nodes="16" buffer_size="1">\n  # (round 0)\n{rows}\n</collective>\n')
+        return p
+
+    return topo, sched
+
+
+CASES = {
+    # name: (transfers, groups, clean radix1, compat radix 1, compat radix 4)
+    "intra": ([(1024, 0, 1, "-1")], 2, 1044, 2067, 2067),
+    "inter": ([(1024, 0, 4, "-1")], 2, 10341, 20571, 20571),
+    "same_port_twice": ([(3, 0, 1, "-1"), (3, 0, 1, "-1")], 2, None, 35, 25),
+    "independent": ([(1, 0, 1, "-1"), (1, 0, 1, "-1"), (1, 2, 3, "-1"), (1, 5, 6, "-1")], 2, None, 29, 21),
+    "independent_inter": ([(2, 4, 0, "-1"), (2, 15, 8, "-1")], 4, 121, 131, 131),
+    "chain": ([(1024, 0, 1, "-1"), (1024, 0, 1, "-1"), (1024, 2, 3, "-1"), (1024, 7, 5, "-1"), (1024, 5, 6, "3"), (1024, 6, 7, "4"), (1024, 3, 2, "2")], 2, 3 * 1044, 6201, 6201),
+    "two_into_one": ([(2, 3, 0, "-1"), (2, 2, 0, "-1")], 2, None, 31, 23),
+    "nic_contention": ([(2, 0, 4, "-1"), (2, 0, 4, "-1")], 2, None, 221, 151),
+    "nic_same_sender": ([(2, 4, 0, "-1"), (2, 4, 8, "-1")], 4, None, 221, 151),
+    "nic_then_dep": ([(5, 0, 4, "-1"), (5, 1, 5, "-1"), (5, 5, 8, "1")], 4, None, 432, 432),
+    "join": ([(2, 0, 4, "-1"), (2, 1, 4, "-1"), (2, 5, 4, "1"), (2, 4, 1, "1,2")], 4, None, 365, 305),
+}
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_simulator_reproduces_recorded_and_classical_numbers(world, name):
+    topo, sched = world
+    transfers, groups, clean, c1, c4 = CASES[name]
+    s, t = sched(transfers, name), topo(groups)
+    assert S.simulate(s, t, radix=1, compat=True) == pytest.approx(c1)
+    assert S.simulate(s, t, radix=4, compat=True) == pytest.approx(c4)
+    if clean is not None:
+        assert S.simulate(s, t, radix=1) == pytest.approx(clean)       # o_s + G(s-1) + L + o_r per hop
+
+
+def test_simulator_cli_and_stats(world, tmp_path):
+    topo, sched = world
+    s, t = sched(CASES["intra"][0], "cli"), topo(2)
+    r = subprocess.run([sys.executable, str(ROOT / "tools/loggp_sim/sim.py"), "--schedule", str(s), "--topo", str(t), "--radix", "1", "--output", str(tmp_path / "o/stats.json")],
+                       capture_output=True, text=True)
+    assert r.returncode == 0 and float(r.stdout.strip()) == pytest.approx(1044e6)
+    assert "finish_time" in (tmp_path / "o/stats.json").read_text()
+
+
+def test_simulator_rejects_bad_schedules(world):
+    topo, sched = world
+    bad = sched([("1024.0", 0, 1, "-1")], "float_size")
+    with pytest.raises(ValueError):
+        S.simulate(bad, topo(2))
+    cyc = sched([(8, 0, 1, "1"), (8, 1, 0, "0")], "cycle")
+    with pytest.raises(RuntimeError):
+        S.simulate(cyc, topo(2))
+
+
+def test_generator_cli_all_combinations_are_well_formed(tmp_path):
+    for coll in ["allgather", "allreduce", "reduce", "bcast", "reduce_scatter"]:
+        for algo in ["ring", "k_ring", "RD", "RM", "PRD", "PRM"]:
+            out = tmp_path / f"{coll}_{algo}.xml"
+            assert gen.main(["--collective", coll, "--num_nodes", "8", "--buffer_size", "8192", "--algorithm", algo, "--k", "2", "--output", str(out)]) == 0
+            root = ET.parse(out).getroot()
+            ts = root.findall("transfer")
+            assert ts and all(int(t.get("size")) > 0 for t in ts)
+            assert root.get("nodes") == "8"
+
+
+def test_generated_schedules_simulate_and_rank_as_the_cost_model_says(tmp_path):
+    # one measured-style profile: L 2 us, g 1 us, 100 GB/s; flat 8-node topology
+    prof = tmp_path / "p.csv"
+    prof.write_text("s,L,o_s,o_r,g,G\n1,2e-6,5e-7,5e-7,1e-6,1e-11\n1073741824,2e-6,5e-7,5e-7,1e-6,1e-11\n")
+    topo = tmp_path / "flat.xml"
+    topo.write_text(S.flat_topology_xml(8, str(prof)))
+    times = {}
+    for algo, k in [("ring", 1), ("PRD", 2), ("PRM", 8)]:
+        for size in [8 * 8, 1 << 30]:
+            out = tmp_path / f"{algo}_{size}.xml"
+            out.write_text(gen.generate("allreduce", 8, size, algo, k))
+            # egress bandwidth is shared on an NVSwitch: one port for large messages, concurrent injection for tiny ones
+            times[(algo, size)] = S.simulate(out, topo, radix=8 if size < 4096 else 1)
+    # latency bound: fewer steps win; bandwidth bound: the ring moves the fewest bytes
+    assert times[("PRM", 64)] < times[("PRD", 64)] < times[("ring", 64)]
+    assert times[("ring", 1 << 30)] < times[("PRD", 1 << 30)] < times[("PRM", 1 << 30)]
+    # 2(n-1)/n * S / beta within 5 % for the ring at 1 GiB
+    assert times[("ring", 1 << 30)] == pytest.approx(2 * 7 / 8 * (1 << 30) * 1e-11, rel=0.05)
+
+
+def test_fitter_round_trip(tmp_path):
+    # synthesise PRTT measurements from known LogGP parameters and recover them
+    L, o_s, o_r, g, G, n, d = 2e-6, 4e-7, 6e-7, 1.5e-6, 1.25e-11, 16, 5e-6
+    rows = ["size n d PRTT(1,0,s) PRTT(n,0,s) PRTT(n,d,s) PRTT_server(n-1,d,s)"]
+    for s in [1, 1024, 65536, 1 << 20, 1 << 24]:
+        p1 = 2 * (L + o_s + o_r + (s - 1) * G)
+        gap = g + (s - 1) * G
+        rows.append(f"{s} {n} {d} {p1} {p1 + (n - 1) * gap} {p1 + (n - 1) * (o_s + d)} {(n - 1) * (o_r + d)}")
+    raw = tmp_path / "raw.csv"
+    raw.write_text("\n".join(rows) + "\n")
+    t = fitter.process_file(raw, tmp_path / "fit.csv")
+    assert t[0, 4] == pytest.approx(g, rel=1e-6) and t[0, 5] == pytest.approx(G, rel=1e-6)
+    assert np.allclose(t[:, 2], o_s) and np.allclose(t[:, 3], o_r)
+    assert t[0, 1] == pytest.approx((2 * (L + o_s + o_r)) / 2)
+    prof = S.Profile(tmp_path / "fit.csv")
+    assert prof("G", 5000) == pytest.approx(G, rel=1e-6)
+
+
+def test_selector_tables(tmp_path):
+    from tools.selector import select
+    prof = tmp_path / "p.csv"
+    prof.write_text("s,L,o_s,o_r,g,G\n1,2e-6,5e-7,5e-7,1e-6,1e-11\n1073741824,2e-6,5e-7,5e-7,1e-6,1e-11\n")
+    out = tmp_path / "tune.csv"
+    assert select.main(["--profile", str(prof), "--ranks", "8", "--min", "8", "--max", str(1 << 28), "--output", str(out)]) == 0
+    rows = [l.split(",") for l in out.read_text().splitlines() if not l.startswith("#")]
+    ar = [r for r in rows if r[0] == "allreduce"]
+    assert ar[0][3] in ("PRM", "PRD") and ar[-1][3] in ("RING", "K_RING")       # latency-optimal first, bandwidth-optimal last
+    assert int(ar[-1][2]) >= 1 << 60
+    bench = tmp_path / "b.csv"
+    bench.write_text("# coll,label,dtype,op,ranks,bytes,iters,time_us,algbw_GBs,busbw_GBs,check\n"
+                     "allreduce,ours-RING-k-1,float,sum,8,8,10,50.0,0,0,ok\nallreduce,ours-PRM-k8,float,sum,8,8,10,9.0,0,0,ok\n"
+                     "allreduce,ours-RING-k-1,float,sum,8,1048576,10,60.0,0,0,ok\nallreduce,ours-PRM-k8,float,sum,8,1048576,10,90.0,0,0,ok\n")
+    assert select.main(["--from-bench", str(bench), "--output", str(out)]) == 0
+    rows = [l.split(",") for l in out.read_text().splitlines() if not l.startswith("#")]
+    assert rows[0][:5] == ["allreduce", "8", "8", "PRM", "8"] and rows[1][3] == "RING"

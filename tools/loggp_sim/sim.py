@@ -1,0 +1,284 @@
+#!/usr/bin/env python
+"""LogGP(+contention) simulator for collective schedules.
+
+    python tools/loggp_sim/sim.py --schedule S.xml --topo T.xml --radix R [--compat] [--output stats.json]
+
+prints one line: the finish time of the last transfer in microseconds (same contract as the
+reference's tools/loggp_sim/sim.py:156-165, which this replaces).  File formats are the
+reference's (tools/loggp_sim/README.md:13-55): schedule XML (<transfer id size src dst deps/>),
+hierarchical topology XML (<group level id param_file [ports]> / <node id>), LogGP CSV
+(s,L,o_s,o_r,g,G; linear interpolation, clamped at both ends).
+
+Model.  A transfer of s bytes from a to b:
+    start (all deps done) -> +o_s -> wait for one of the `radix` send ports of a (and, if a and b are
+    in different level-0 groups, one of the source group's NICs) -> the bytes take G(s-1) ->
+    +L -> wait for the destination group's NIC / a receive port of b -> +o_r -> done.
+  default ("clean", the classical LogGP of the fixture comments): the per-byte term is charged
+    once (done = start + o_s + G(s-1) + L + o_r when nothing is contended), consecutive messages
+    on a port are at least max(g, G s) apart, a NIC is busy for G s per message.  Optional
+    --gamma adds a reduction cost per received byte, --alpha a fixed cost per transfer (kernel
+    launch of the reference's one-launch-per-step design).
+  --compat reproduces the behaviour of the simulator the reference ships, including its quirks:
+    G(s-1) is charged on the send side and again on the receive side; the send gap g counts from
+    the END of the previous send on the port, the receive gap from the START of the previous
+    receive; a NIC is busy for G s.
+Large transfers cost the same closed form (no per-4-KiB events), so 1 GiB schedules simulate
+instantly.
+"""
+from __future__ import annotations
+
+import argparse
+import heapq
+import json
+import sys
+import xml.etree.ElementTree as ET
+from dataclasses import dataclass, field
+from pathlib import Path
+
+import numpy as np
+
+REPO = Path(__file__).resolve().parents[2]
+
+
+def get_path(p: str) -> Path:
+    q = Path(p)
+    if q.is_absolute() or q.exists():
+        return q
+    return REPO / p
+
+
+# ------------------------------------------------------------------ inputs
+@dataclass
+class Task:
+    id: int
+    src: int
+    dst: int
+    size: int
+    deps: set
+    children: list = field(default_factory=list)
+    start: float = -1.0
+    done: float = -1.0
+
+
+def parse_schedule(path) -> tuple[dict, dict]:
+    # free text such as "# (round 3)" between the elements is character data and is ignored
+    root = ET.parse(get_path(str(path))).getroot()
+    tasks: dict[int, Task] = {}
+    for t in root.iter("transfer"):
+        size = t.get("size")
+        try:
+            nbytes = int(size)
+        except (TypeError, ValueError):
+            raise ValueError(f"transfer {t.get('id')}: size {size!r} is not an integer")
+        deps = {int(d) for d in (t.get("deps") or "-1").split(",") if d.strip() and int(d) >= 0}
+        tid = int(t.get("id"))
+        if tid in tasks:
+            raise ValueError(f"duplicate transfer id {tid}")
+        tasks[tid] = Task(tid, int(t.get("src")), int(t.get("dst")), nbytes, deps)
+    for t in tasks.values():
+        for d in t.deps:
+            if d not in tasks:
+                raise ValueError(f"transfer {t.id} depends on unknown transfer {d}")
+            tasks[d].children.append(t.id)
+    return tasks, dict(root.attrib)
+
+
+class Profile:
+    """One LogGP CSV, interpolated per parameter."""
+
+    def __init__(self, path):
+        data = np.genfromtxt(get_path(str(path)), delimiter=",", names=True)
+        data = np.atleast_1d(data)
+        self.s = np.asarray(data["s"], dtype=float)
+        order = np.argsort(self.s)
+        self.s = self.s[order]
+        self.cols = {k: np.asarray(data[k], dtype=float)[order] for k in ("L", "o_s", "o_r", "g", "G")}
+
+    def __call__(self, name: str, size: float) -> float:
+        return float(np.interp(size, self.s, self.cols[name]))
+
+
+@dataclass
+class Topology:
+    nodes: list
+    group0: dict                 # node -> level-0 group key
+    nics: dict                   # level-0 group key -> NIC count (None: unlimited)
+    chain: dict                  # node -> list of (level, group key, param file) from innermost outwards
+
+    def pair_profile_file(self, a: int, b: int) -> str:
+        keys_b = {k for _, k, _ in self.chain[b]}
+        for _, k, f in self.chain[a]:
+            if k in keys_b:
+                return f
+        raise ValueError(f"nodes {a} and {b} share no group")
+
+
+def parse_topology(path) -> Topology:
+    root = ET.parse(get_path(str(path))).getroot()
+    nodes, group0, nics, chain = [], {}, {}, {}
+
+    def walk(el, stack):
+        for ch in el:
+            if ch.tag == "group":
+                key = (int(ch.get("level")), ch.get("id"), len(stack), id(ch))
+                entry = (int(ch.get("level")), key, ch.get("param_file"))
+                if int(ch.get("level")) == 0:
+                    p = ch.get("ports")
+                    nics[key] = int(p) if p is not None and int(p) > 0 else None
+                walk(ch, stack + [entry])
+            elif ch.tag == "node":
+                n = int(ch.get("id"))
+                nodes.append(n)
+                chain[n] = list(reversed(stack))
+                lvl0 = [e for e in stack if e[0] == 0]
+                group0[n] = lvl0[-1][1] if lvl0 else ("flat",)
+
+    walk(root, [])
+    return Topology(sorted(nodes), group0, nics, chain)
+
+
+def flat_topology_xml(n: int, param_file: str) -> str:
+    nodes = "".join(f'<node id="{i}"/>' for i in range(n))
+    return f'<topo num_nodes="{n}" num_levels="1"><group level="0" id="0" param_file="{param_file}">{nodes}</group></topo>'
+
+
+# ------------------------------------------------------------------ engine
+class Ports:
+    """`count` interchangeable ports with a minimum spacing between uses."""
+
+    def __init__(self, count):
+        self.free = [0.0] * count          # busy until
+        self.mark = [-1e300] * count       # reference point of the gap rule (start or end of the last use)
+
+    def reserve(self, t: float, gap: float):
+        """earliest (time, port) at which a use may start for a request made at t"""
+        best, bi = None, 0
+        for i in range(len(self.free)):
+            s = max(t, self.free[i], self.mark[i] + gap)
+            if best is None or s < best:
+                best, bi = s, i
+        return best, bi
+
+
+class Simulator:
+    def __init__(self, schedule, topo, radix: int = 1, compat: bool = False, gamma: float = 0.0, alpha: float = 0.0):
+        self.tasks, self.meta = parse_schedule(schedule) if not isinstance(schedule, dict) else (schedule, {})
+        self.topo = parse_topology(topo) if not isinstance(topo, Topology) else topo
+        self.radix, self.compat, self.gamma, self.alpha = radix, compat, gamma, alpha
+        self.profiles: dict[str, Profile] = {}
+        self.send = {n: Ports(radix) for n in self.topo.nodes}
+        self.recv = {n: Ports(radix) for n in self.topo.nodes}
+        self.nic_s = {k: Ports(c) for k, c in self.topo.nics.items() if c}
+        self.nic_r = {k: Ports(c) for k, c in self.topo.nics.items() if c}
+        self.stats = {"send_wait": 0.0, "recv_wait": 0.0, "nic_wait": 0.0}
+        for t in self.tasks.values():
+            for n in (t.src, t.dst):
+                if n not in self.send:
+                    raise ValueError(f"transfer {t.id} uses node {n}, which is not in the topology")
+
+    def prof(self, a, b) -> Profile:
+        f = self.topo.pair_profile_file(a, b)
+        if f not in self.profiles:
+            self.profiles[f] = Profile(f)
+        return self.profiles[f]
+
+    def run(self) -> float:
+        q: list = []
+        seq = 0
+
+        def post(t, stage, task):
+            nonlocal seq
+            heapq.heappush(q, (t, seq, stage, task.id))
+            seq += 1
+
+        remaining = {t.id: len(t.deps) for t in self.tasks.values()}
+        for t in self.tasks.values():
+            if not t.deps:
+                post(0.0, 0, t)
+        finished, last = 0, 0.0
+        arrive_state = {}
+        while q:
+            now, _, stage, tid = heapq.heappop(q)
+            task = self.tasks[tid]
+            p = self.prof(task.src, task.dst)
+            s = task.size
+            G, g = p("G", s), p("g", s)
+            wire = G * max(s - 1, 0)
+            inter = self.topo.group0[task.src] != self.topo.group0[task.dst]
+            if stage == 0:                                   # dependencies done: sender overhead
+                task.start = now
+                post(now + self.alpha + p("o_s", s), 1, task)
+            elif stage == 1:                                 # inject: send port (+ source NIC)
+                gap = g if self.compat else max(g, G * s)
+                st, pi = self.send[task.src].reserve(now, gap)
+                nic = self.nic_s.get(self.topo.group0[task.src]) if inter else None
+                if nic is not None:
+                    ns, ni = nic.reserve(st, 0.0)
+                    self.stats["nic_wait"] += ns - st
+                    st = ns
+                    nic.free[ni] = st + G * s
+                self.stats["send_wait"] += st - now
+                ports = self.send[task.src]
+                ports.free[pi] = st + wire
+                ports.mark[pi] = st + wire if self.compat else st
+                arrive_state[tid] = st
+                post(st + wire + p("L", s), 2, task)
+            elif stage == 2:                                 # arrival: destination NIC, receive port
+                gap = g if self.compat else max(g, G * s)
+                st, pi = self.recv[task.dst].reserve(now, gap)
+                nic = self.nic_r.get(self.topo.group0[task.dst]) if inter else None
+                if nic is not None:
+                    ns, ni = nic.reserve(st, 0.0)
+                    self.stats["nic_wait"] += ns - st
+                    st = ns
+                    nic.free[ni] = st + G * s
+                self.stats["recv_wait"] += st - now
+                ports = self.recv[task.dst]
+                busy = wire if self.compat else 0.0          # the classical model charges the bytes once
+                ports.free[pi] = st + busy
+                ports.mark[pi] = st
+                post(st + busy + p("o_r", s) + self.gamma * s, 3, task)
+            else:                                            # done
+                task.done = now
+                last = max(last, now)
+                finished += 1
+                for c in task.children:
+                    remaining[c] -= 1
+                    if remaining[c] == 0:
+                        post(now, 0, self.tasks[c])
+        if finished != len(self.tasks):
+            raise RuntimeError("Not all tasks completed (dependency cycle in the schedule?)")
+        return last
+
+    def output_stats(self, path) -> None:
+        out = {"finish_time": max((t.done for t in self.tasks.values()), default=0.0), **self.stats,
+               "tasks": {str(t.id): {"start": t.start, "done": t.done, "src": t.src, "dst": t.dst, "size": t.size} for t in self.tasks.values()}}
+        Path(path).parent.mkdir(parents=True, exist_ok=True)
+        Path(path).write_text(json.dumps(out, indent=1))
+
+
+def simulate(schedule, topo, radix=1, compat=False, gamma=0.0, alpha=0.0) -> float:
+    """Finish time in the time unit of the parameter files (seconds for measured profiles)."""
+    return Simulator(schedule, topo, radix, compat, gamma, alpha).run()
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description="LogGP collective schedule simulator")
+    ap.add_argument("--schedule", required=True)
+    ap.add_argument("--topo", required=True)
+    ap.add_argument("--radix", type=int, default=1, help="concurrent send ports and receive ports per device")
+    ap.add_argument("--compat", action="store_true", help="reproduce the cost accounting of the simulator shipped with the reference")
+    ap.add_argument("--gamma", type=float, default=0.0, help="reduction cost per received byte")
+    ap.add_argument("--alpha", type=float, default=0.0, help="fixed cost per transfer")
+    ap.add_argument("--output", default=None, help="write per-transfer times and contention statistics (JSON)")
+    a = ap.parse_args(argv)
+    sim = Simulator(a.schedule, a.topo, a.radix, a.compat, a.gamma, a.alpha)
+    t = sim.run()
+    if a.output:
+        sim.output_stats(a.output)
+    print(t * 1e6)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
