@@ -26,7 +26,8 @@ constexpr int kMaxBlock = 512;
 struct RankCtx {
   int rank, nranks, max_cta, nslot;
   long long slot_bytes;
-  long long tail_off, head_off, scratch_off, fifo_off, heap_bytes;
+  long long tail_off, head_off, ll_off, scratch_off, fifo_off, heap_bytes;
+  long long ll_slot_bytes;                // bytes of one low-latency slot (2 x the largest payload)
   long long scratch_bytes;
   char* heap[kMaxRanks];                  // every rank's heap as mapped in this process
   unsigned long long* sent;               // [nranks * max_cta] entries pushed per (peer, cta)
@@ -53,6 +54,25 @@ struct KernelArgs {
   unsigned long long timeout_ns;
   LaunchRank r[kMaxVRanks];
 };
+
+// ---- low-latency all-reduce (ll_allreduce.cu)
+constexpr int kLLMaxSteps = 6;
+constexpr int kLLBlock = 256;
+struct LLRank { RankCtx* ctx; const void* in; void* out; };
+struct LLArgs {
+  int n_vrank, n_cta, nsteps, avg;
+  float scale;
+  unsigned epoch;
+  unsigned long long timeout_ns;
+  long long count;
+  uint8_t npeers[kLLMaxSteps];
+  uint8_t peers[kMaxVRanks][kLLMaxSteps][kMaxActionPeers];     // ascending rank
+  uint8_t self_pos[kMaxVRanks][kLLMaxSteps];                   // partners with a rank below mine
+  LLRank r[kMaxVRanks];
+};
+typedef void (*LLKernelFn)(LLArgs);
+LLKernelFn ll_kernel_for(int dtype, int op);
+int ll_lines_per_cta();
 
 // dtype index used by the launcher tables (order of ncclDataType_t)
 enum DType : int { DT_I8 = 0, DT_U8 = 1, DT_I32 = 2, DT_U32 = 3, DT_I64 = 4, DT_U64 = 5, DT_F16 = 6, DT_F32 = 7, DT_F64 = 8, DT_BF16 = 9, DT_COUNT = 10 };

@@ -120,34 +120,50 @@ static __device__ __noinline__ bool wait_counter(const unsigned long long* flag,
 }
 
 // ---------------------------------------------------------------- data movement
-// value = reduce(src[0..nsrc)) -> dst[0..ndst); `local_src` (index or -1) is the
+// value = reduce(src[0..NSRC)) -> dst[0..NDST); `local_src` (index or -1) is the
 // user-buffer operand (plain loads, optional scaling); the other sources are FIFO slots.
-template <typename T, int OP, int U>
-__device__ __forceinline__ void reduce_copy_vec(int nsrc, const char* const* src, int local_src, int ndst, char* const* dst,
-                                                long long npack, bool do_scale, float scale) {
+// NSRC / NDST > 0: compile-time operand counts (pointers stay in registers, loops unroll);
+// 0: run-time counts (generic path for wide radices).
+// Both loops run an unpredicated main part (all U packs of a thread in range) and finish the
+// remainder one pack at a time, which keeps the register count of the main part low.
+template <int U, int NDST>
+__device__ __forceinline__ void copy_vec(const char* src, bool src_local, int ndst_rt, char* const* dst, long long first, long long npack) {
+  const int ndst = NDST ? NDST : ndst_rt;
+  const long long nt = blockDim.x;
+  // whole super-blocks of nt * U packs; the rest is done one pack per thread at a time
+  const long long done = (U == 1) ? npack : first + ((npack - first) / (nt * U)) * (nt * U);
+  for (long long base = first + threadIdx.x; base < done; base += nt * U) {
+    uint4 v[U];
+    const char* sp = src + base * 16;
+#pragma unroll
+    for (int u = 0; u < U; u++) v[u] = src_local ? ld_local(sp + u * nt * 16) : ld_slot(sp + u * nt * 16);
+#pragma unroll
+    for (int d = 0; d < (NDST ? NDST : kMaxActionPeers + 1); d++) {
+      if (d < ndst) {
+        char* dp = dst[d] + base * 16;
+#pragma unroll
+        for (int u = 0; u < U; u++) st_vec(dp + u * nt * 16, v[u]);
+      }
+    }
+  }
+  if (U > 1 && done < npack) copy_vec<1, NDST>(src, src_local, ndst_rt, dst, done, npack);
+}
+
+template <typename T, int OP, int U, int NSRC, int NDST>
+__device__ __forceinline__ void reduce_copy_vec(int nsrc_rt, const char* const* src, int local_src, int ndst_rt, char* const* dst,
+                                                long long first, long long npack, bool do_scale, float scale) {
   typedef typename AccOf<T>::type A;
   constexpr int N = Pack<T>::N;
-  const int nt = blockDim.x;
-  for (long long base = threadIdx.x; base < npack; base += (long long)nt * U) {
-    if (nsrc == 1 && !do_scale) {           // pure copy: no conversion
-      uint4 v[U];
+  const int nsrc = NSRC ? NSRC : nsrc_rt, ndst = NDST ? NDST : ndst_rt;
+  const long long nt = blockDim.x;
+  const long long done = (U == 1) ? npack : first + ((npack - first) / (nt * U)) * (nt * U);
+  for (long long base = first + threadIdx.x; base < done; base += nt * U) {
+    A acc[U][N];
+    {
+      const char* sp = src[0] + base * 16;
 #pragma unroll
       for (int u = 0; u < U; u++) {
-        long long i = base + (long long)u * nt;
-        if (i < npack) v[u] = (local_src == 0) ? ld_local(src[0] + i * 16) : ld_slot(src[0] + i * 16);
-      }
-      for (int d = 0; d < ndst; d++) {
-#pragma unroll
-        for (int u = 0; u < U; u++) { long long i = base + (long long)u * nt; if (i < npack) st_vec(dst[d] + i * 16, v[u]); }
-      }
-      continue;
-    }
-    A acc[U][N];
-#pragma unroll
-    for (int u = 0; u < U; u++) {
-      long long i = base + (long long)u * nt;
-      if (i < npack) {
-        uint4 v = (local_src == 0) ? ld_local(src[0] + i * 16) : ld_slot(src[0] + i * 16);
+        uint4 v = (local_src == 0) ? ld_local(sp + u * nt * 16) : ld_slot(sp + u * nt * 16);
         Pack<T>::up(v, acc[u]);
         if (do_scale && local_src == 0) {
 #pragma unroll
@@ -155,17 +171,15 @@ __device__ __forceinline__ void reduce_copy_vec(int nsrc, const char* const* src
         }
       }
     }
-    for (int s = 1; s < nsrc; s++) {
-      uint4 v[U];
 #pragma unroll
-      for (int u = 0; u < U; u++) {
-        long long i = base + (long long)u * nt;
-        if (i < npack) v[u] = (local_src == s) ? ld_local(src[s] + i * 16) : ld_slot(src[s] + i * 16);
-      }
+    for (int s = 1; s < (NSRC ? NSRC : kMaxActionPeers + 1); s++) {
+      if (s < nsrc) {
+        uint4 v[U];
+        const char* sp = src[s] + base * 16;
 #pragma unroll
-      for (int u = 0; u < U; u++) {
-        long long i = base + (long long)u * nt;
-        if (i < npack) {
+        for (int u = 0; u < U; u++) v[u] = (local_src == s) ? ld_local(sp + u * nt * 16) : ld_slot(sp + u * nt * 16);
+#pragma unroll
+        for (int u = 0; u < U; u++) {
           A x[N]; Pack<T>::up(v[u], x);
 #pragma unroll
           for (int e = 0; e < N; e++) {
@@ -175,19 +189,40 @@ __device__ __forceinline__ void reduce_copy_vec(int nsrc, const char* const* src
         }
       }
     }
-    for (int d = 0; d < ndst; d++) {
 #pragma unroll
-      for (int u = 0; u < U; u++) {
-        long long i = base + (long long)u * nt;
-        if (i < npack) st_vec(dst[d] + i * 16, Pack<T>::down(acc[u]));
+    for (int d = 0; d < (NDST ? NDST : kMaxActionPeers + 1); d++) {
+      if (d < ndst) {
+        char* dp = dst[d] + base * 16;
+#pragma unroll
+        for (int u = 0; u < U; u++) st_vec(dp + u * nt * 16, Pack<T>::down(acc[u]));
       }
     }
   }
+  if (U > 1 && done < npack) reduce_copy_vec<T, OP, 1, NSRC, NDST>(nsrc_rt, src, local_src, ndst_rt, dst, done, npack, do_scale, scale);
+}
+
+// Picks the instantiation for the common operand counts of ring / pairwise schedules.
+template <typename T, int OP>
+__device__ __noinline__ void reduce_copy_dispatch(int nsrc, const char* const* src, int local_src, int ndst, char* const* dst,
+                                                     long long npack, bool do_scale, float scale) {
+  constexpr int N = Pack<T>::N;
+  // 16-byte packs in flight per thread: 8 when only moving data; for reductions bounded by the accumulator registers
+  constexpr int UR = (sizeof(typename AccOf<T>::type) * N * 4 <= 128) ? 4 : 2;
+  if (nsrc == 1 && !do_scale) {
+    if (ndst == 1) copy_vec<8, 1>(src[0], local_src == 0, 1, dst, 0, npack);
+    else if (ndst == 2) copy_vec<8, 2>(src[0], local_src == 0, 2, dst, 0, npack);
+    else copy_vec<4, 0>(src[0], local_src == 0, ndst, dst, 0, npack);
+    return;
+  }
+  if (nsrc == 1 && ndst == 1) reduce_copy_vec<T, OP, UR, 1, 1>(1, src, local_src, 1, dst, 0, npack, do_scale, scale);
+  else if (nsrc == 2 && ndst == 1) reduce_copy_vec<T, OP, UR, 2, 1>(2, src, local_src, 1, dst, 0, npack, do_scale, scale);
+  else if (nsrc == 2 && ndst == 2) reduce_copy_vec<T, OP, UR, 2, 2>(2, src, local_src, 2, dst, 0, npack, do_scale, scale);
+  else reduce_copy_vec<T, OP, (UR > 2 ? 2 : UR), 0, 0>(nsrc, src, local_src, ndst, dst, 0, npack, do_scale, scale);
 }
 
 // Element-wise path: unaligned user buffers and the last, partial pack of an action.
 template <typename T, int OP>
-__device__ __forceinline__ void reduce_copy_elem(int nsrc, const char* const* src, int local_src, int ndst, char* const* dst,
+__device__ __noinline__ void reduce_copy_elem(int nsrc, const char* const* src, int local_src, int ndst, char* const* dst,
                                                  long long first, long long nelem, bool do_scale, float scale) {
   typedef typename AccOf<T>::type A;
   for (long long i = first + threadIdx.x; i < nelem; i += blockDim.x) {
@@ -205,43 +240,55 @@ __device__ __forceinline__ void reduce_copy_elem(int nsrc, const char* const* sr
 }
 
 // ---------------------------------------------------------------- the kernel
+constexpr int kSliceCache = 192;      // actions whose CTA slice is precomputed in shared memory
+
 template <typename T, int OP>
 __global__ void __launch_bounds__(kMaxBlock, 1) exec_kernel(const KernelArgs ka) {
   const int vr = blockIdx.x / ka.n_cta, cta = blockIdx.x % ka.n_cta;
   const LaunchRank& L = ka.r[vr];
   RankCtx* __restrict__ ctx = L.ctx;
   const int tid = threadIdx.x;
-  const int rank = ctx->rank, nranks = ctx->nranks, max_cta = ctx->max_cta, nslot = ctx->nslot;
-  const long long slot_bytes = ctx->slot_bytes;
-  char* const my_heap = ctx->heap[rank];
   constexpr int esz = (int)sizeof(T);
 
   __shared__ int s_send_slot[kMaxRanks], s_recv_slot[kMaxRanks];
+  __shared__ char* s_heap[kMaxRanks];
+  __shared__ long long s_lo[kSliceCache], s_hi[kSliceCache];
   __shared__ int s_fail, s_maxseg;
 
+  // everything read from the context more than once is fetched once, in parallel
+  const int rank = ctx->rank, nranks = ctx->nranks, max_cta = ctx->max_cta, nslot = ctx->nslot;
+  const long long slot_bytes = ctx->slot_bytes, tail_off = ctx->tail_off, head_off = ctx->head_off, fifo_off = ctx->fifo_off, scratch_off = ctx->scratch_off;
   // thread p (< nranks) owns the two counters of the connections with peer p
   unsigned long long my_sent = 0, my_rcvd = 0;
-  if (tid < nranks) { my_sent = ctx->sent[tid * max_cta + cta]; my_rcvd = ctx->rcvd[tid * max_cta + cta]; }
+  if (tid < nranks) { s_heap[tid] = ctx->heap[tid]; my_sent = ctx->sent[tid * max_cta + cta]; my_rcvd = ctx->rcvd[tid * max_cta + cta]; }
   if (tid == 0) { s_fail = 0; s_maxseg = 0; }
   __syncthreads();
+  const long long seg_elems = (slot_bytes / 16) * (esz >= 16 ? 1 : 16 / esz);
   {
     int m = 0;
-    for (int ai = tid; ai < L.n_actions; ai += blockDim.x) m = max(m, slice_of(L.actions[ai].count, esz, cta, ka.n_cta, slot_bytes).nseg);
+    for (int ai = tid; ai < L.n_actions; ai += blockDim.x) {
+      const Slice sl = slice_of(L.actions[ai].count, esz, cta, ka.n_cta, slot_bytes);
+      if (ai < kSliceCache) { s_lo[ai] = sl.lo; s_hi[ai] = sl.hi; }
+      m = max(m, sl.nseg);
+    }
     if (m) atomicMax(&s_maxseg, m);
   }
   __syncthreads();
   const int maxseg = s_maxseg;
+  char* const my_heap = s_heap[rank];
   WaitCtx w; w.ctx = ctx; w.timeout_ns = ka.timeout_ns; w.cta = cta;
   bool failed = false;
 
   for (int seg = 0; seg < maxseg && !failed; seg++) {
     for (int ai = 0; ai < L.n_actions; ai++) {
-      const Action ac = L.actions[ai];
-      const Slice sl = slice_of(ac.count, esz, cta, ka.n_cta, slot_bytes);
-      if (seg >= sl.nseg) continue;
-      const long long lo = sl.lo + (long long)seg * sl.seg_elems;
-      const long long hi = (lo + sl.seg_elems < sl.hi) ? lo + sl.seg_elems : sl.hi;
+      long long sl_lo, sl_hi;
+      if (ai < kSliceCache) { sl_lo = s_lo[ai]; sl_hi = s_hi[ai]; }
+      else { const Slice sl = slice_of(L.actions[ai].count, esz, cta, ka.n_cta, slot_bytes); sl_lo = sl.lo; sl_hi = sl.hi; }
+      const long long lo = sl_lo + (long long)seg * seg_elems;
+      if (lo >= sl_hi) continue;
+      const long long hi = (lo + seg_elems < sl_hi) ? lo + seg_elems : sl_hi;
       const long long len = hi - lo;
+      const Action ac = L.actions[ai];
 
       // ---- wait: credit on every send connection, data on every receive connection
       if (tid < nranks) {
@@ -250,12 +297,12 @@ __global__ void __launch_bounds__(kMaxBlock, 1) exec_kernel(const KernelArgs ka)
         for (int j = 0; j < ac.n_send; j++) if (ac.send_peer[j] == tid) {
           s_send_slot[tid] = (int)(my_sent % (unsigned)nslot);
           if (my_sent + 1 > (unsigned long long)nslot)
-            ok = wait_counter(reinterpret_cast<const unsigned long long*>(my_heap + ctx->head_off + (long long)(tid * max_cta + cta) * kFlagStride),
+            ok = wait_counter(reinterpret_cast<const unsigned long long*>(my_heap + head_off + (long long)(tid * max_cta + cta) * kFlagStride),
                               my_sent + 1 - nslot, w, 1, tid);
         }
         for (int j = 0; j < ac.n_recv && ok; j++) if (ac.recv_peer[j] == tid) {
           s_recv_slot[tid] = (int)(my_rcvd % (unsigned)nslot);
-          ok = wait_counter(reinterpret_cast<const unsigned long long*>(my_heap + ctx->tail_off + (long long)(tid * max_cta + cta) * kFlagStride),
+          ok = wait_counter(reinterpret_cast<const unsigned long long*>(my_heap + tail_off + (long long)(tid * max_cta + cta) * kFlagStride),
                             my_rcvd + 1, w, 2, tid);
         }
         if (!ok) s_fail = 1;
@@ -268,34 +315,40 @@ __global__ void __launch_bounds__(kMaxBlock, 1) exec_kernel(const KernelArgs ka)
       int nsrc = 0, ndst = 0, local_src = -1;
       bool aligned = true;
       const bool has_src = ac.src_buf != BUF_NONE;
-      for (int j = 0; j <= ac.n_recv; j++) {
-        if (j == ac.self_pos && has_src) {
-          const char* base = ac.src_buf == BUF_IN ? (const char*)L.in : ac.src_buf == BUF_OUT ? (const char*)L.out : my_heap + ctx->scratch_off;
-          src[nsrc] = base + (ac.src_off + lo) * esz;
-          aligned &= ((reinterpret_cast<uintptr_t>(src[nsrc]) & 15) == 0);
-          local_src = nsrc++;
-        }
-        if (j < ac.n_recv) {
-          const int p = ac.recv_peer[j];
-          src[nsrc++] = my_heap + ctx->fifo_off + ((long long)(p * max_cta + cta) * nslot + s_recv_slot[p]) * slot_bytes;
+#pragma unroll
+      for (int j = 0; j <= kMaxActionPeers; j++) {
+        if (j <= ac.n_recv) {
+          if (j == ac.self_pos && has_src) {
+            const char* base = ac.src_buf == BUF_IN ? (const char*)L.in : ac.src_buf == BUF_OUT ? (const char*)L.out : my_heap + scratch_off;
+            src[nsrc] = base + (ac.src_off + lo) * esz;
+            aligned &= ((reinterpret_cast<uintptr_t>(src[nsrc]) & 15) == 0);
+            local_src = nsrc++;
+          }
+          if (j < ac.n_recv) {
+            const int p = ac.recv_peer[j];
+            src[nsrc++] = my_heap + fifo_off + ((long long)(p * max_cta + cta) * nslot + s_recv_slot[p]) * slot_bytes;
+          }
         }
       }
       if (ac.dst_buf != BUF_NONE) {
-        char* base = ac.dst_buf == BUF_OUT ? (char*)L.out : my_heap + ctx->scratch_off;
+        char* base = ac.dst_buf == BUF_OUT ? (char*)L.out : my_heap + scratch_off;
         dst[ndst] = base + (ac.dst_off + lo) * esz;
         aligned &= ((reinterpret_cast<uintptr_t>(dst[ndst]) & 15) == 0);
         ndst++;
       }
-      for (int j = 0; j < ac.n_send; j++) {
-        const int p = ac.send_peer[j];
-        dst[ndst++] = ctx->heap[p] + ctx->fifo_off + ((long long)(rank * max_cta + cta) * nslot + s_send_slot[p]) * slot_bytes;
+#pragma unroll
+      for (int j = 0; j < kMaxActionPeers; j++) {
+        if (j < ac.n_send) {
+          const int p = ac.send_peer[j];
+          dst[ndst++] = s_heap[p] + fifo_off + ((long long)(rank * max_cta + cta) * nslot + s_send_slot[p]) * slot_bytes;
+        }
       }
       const bool do_scale = ka.avg && (ac.flags & ACT_SCALE_SRC) && local_src >= 0;
 
       // ---- one pass over the segment
       constexpr int N = Pack<T>::N;
       long long nfull = aligned ? len / N : 0;
-      if (nfull) reduce_copy_vec<T, OP, 4>(nsrc, src, local_src, ndst, dst, nfull, do_scale, ka.scale);
+      if (nfull) reduce_copy_dispatch<T, OP>(nsrc, src, local_src, ndst, dst, nfull, do_scale, ka.scale);
       if (nfull * N < len) reduce_copy_elem<T, OP>(nsrc, src, local_src, ndst, dst, nfull * N, len, do_scale, ka.scale);
       __syncthreads();
 
@@ -303,11 +356,11 @@ __global__ void __launch_bounds__(kMaxBlock, 1) exec_kernel(const KernelArgs ka)
       if (tid < nranks) {
         for (int j = 0; j < ac.n_send; j++) if (ac.send_peer[j] == tid) {
           my_sent++;
-          st_release_sys(reinterpret_cast<unsigned long long*>(ctx->heap[tid] + ctx->tail_off + (long long)(rank * max_cta + cta) * kFlagStride), my_sent);
+          st_release_sys(reinterpret_cast<unsigned long long*>(s_heap[tid] + tail_off + (long long)(rank * max_cta + cta) * kFlagStride), my_sent);
         }
         for (int j = 0; j < ac.n_recv; j++) if (ac.recv_peer[j] == tid) {
           my_rcvd++;
-          st_release_sys(reinterpret_cast<unsigned long long*>(ctx->heap[tid] + ctx->head_off + (long long)(rank * max_cta + cta) * kFlagStride), my_rcvd);
+          st_release_sys(reinterpret_cast<unsigned long long*>(s_heap[tid] + head_off + (long long)(rank * max_cta + cta) * kFlagStride), my_rcvd);
         }
       }
     }

@@ -16,171 +16,66 @@
 #include <map>
 #include <mutex>
 #include <tuple>
-#include "../include/sm100_ptx.cuh"
+#include "../include/sm100_gemm.cuh"
 
 namespace piccl_ops {
 
 using namespace sm100;
 typedef __nv_bfloat16 bf16;
 
-constexpr int BM = 128, BK = 64;
-constexpr unsigned long long kWaitLimitNs = 4000000000ull;   // 4 s
-
-template <int BN, int STAGES>
-struct SmemLayout {
-  static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
-  static constexpr int TOTAL = BAR_OFF + (2 * STAGES + 4) * 8 + 16;
-};
+constexpr int BM = GEMM_BM, BK = GEMM_BK;
+template <int BN, int STAGES> using SmemLayout = GemmSmem<BN, STAGES>;
 
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
   return 0.5f * x * (1.f + tanhf(k0 * (x + k1 * x * x * x)));
 }
 
+// Plain GEMM: tiles in m-fastest order, nothing to wait for, bias / GELU epilogue.
+template <int BN>
+struct PlainPolicy {
+  const CUtensorMap* ta; bf16* C; bf16* C_pre; const bf16* bias; int N, num_m, num_n, act_gelu;
+  __device__ int num_tiles() const { return num_m * num_n; }
+  __device__ void tile(int idx, int& m_blk, int& n_blk) const { m_blk = idx % num_m; n_blk = idx / num_m; }
+  __device__ const CUtensorMap* a_map(int m_blk, int& row0) const { row0 = m_blk * BM; return ta; }
+  __device__ bool gate(int, volatile int*) const { return true; }
+  __device__ bool tile_begin(int, int, int, volatile int*) { return true; }
+  __device__ void tile_end(int, int, int) {}
+  __device__ void store(int m_blk, int n_blk, int row, int col0, float (&v)[32]) {
+    const size_t off = (size_t)(m_blk * BM + row) * N + (size_t)n_blk * BN + col0;
+    if (bias) {
+      const bf16* brow = bias + (size_t)n_blk * BN + col0;
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) {
+        uint4 bb = *reinterpret_cast<const uint4*>(brow + i);
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bb);
+#pragma unroll
+        for (int j = 0; j < 4; j++) { float2 f = __bfloat1622float2(b2[j]); v[i + 2 * j] += f.x; v[i + 2 * j + 1] += f.y; }
+      }
+    }
+    if (C_pre) store_row32_bf16(C_pre + off, v);
+    if (act_gelu) {
+#pragma unroll
+      for (int i = 0; i < 32; i++) {
+        // activation of the value as stored (bf16), so that backward sees the same pre-activation
+        float x = C_pre ? __bfloat162float(__float2bfloat16_rn(v[i])) : v[i];
+        v[i] = gelu_tanh(x);
+      }
+    }
+    store_row32_bf16(C + off, v);
+  }
+};
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_nt_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, bf16* __restrict__ C, bf16* __restrict__ C_pre,
                     const bf16* __restrict__ bias, int M, int N, int K, int act_gelu, int* __restrict__ status) {
-  typedef SmemLayout<BN, STAGES> L;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  // the 128-byte swizzle needs 1024-byte aligned tiles
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
-  uint64_t* empty = full + STAGES;
-  uint64_t* tmem_full = empty + STAGES;
-  uint64_t* tmem_empty = tmem_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   __shared__ int s_abort;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_m = M / BM, num_n = N / BN, num_tiles = num_m * num_n, num_kb = K / BK;
-  constexpr uint32_t TMEM_COLS = 2 * BN;           // 256 or 512: a power of two
-
-  if (threadIdx.x == 0) {
-    s_abort = 0;
-    for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; a++) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 128); }
-    fence_barrier_init();
-  }
-  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmap_a); tma_prefetch_desc(&tmap_b); }
-  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  if (warp == 0) {
-    // ------------------------------------------------------------ producer
-    if (lane == 0) {
-      int stage = 0; uint32_t phase = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && !s_abort; tile += gridDim.x) {
-        const int m_blk = tile % num_m, n_blk = tile / num_m;
-        for (int kb = 0; kb < num_kb; kb++) {
-          if (!mbar_wait(&empty[stage], phase ^ 1, &s_abort, kWaitLimitNs)) { atomicExch(status, 1); break; }
-          uint8_t* sa = smem + stage * L::STAGE_BYTES; uint8_t* sb = sa + L::A_BYTES;
-          mbar_arrive_expect_tx(&full[stage], L::STAGE_BYTES);
-          tma_load_2d(sa, &tmap_a, kb * BK, m_blk * BM, &full[stage]);
-          tma_load_2d(sb, &tmap_b, kb * BK, n_blk * BN, &full[stage]);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN);
-      int stage = 0; uint32_t phase = 0; int local = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && !s_abort; tile += gridDim.x, local++) {
-        const int acc = local & 1; const uint32_t acc_phase = (local >> 1) & 1;
-        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, &s_abort, kWaitLimitNs)) { atomicExch(status, 2); break; }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        bool ok = true;
-        for (int kb = 0; kb < num_kb; kb++) {
-          if (!mbar_wait(&full[stage], phase, &s_abort, kWaitLimitNs)) { atomicExch(status, 3); ok = false; break; }
-          tc_fence_after();
-          const uint8_t* sa = smem + stage * L::STAGE_BYTES; const uint8_t* sb = sa + L::A_BYTES;
-          const uint64_t da = make_smem_desc_k128(sa), db = make_smem_desc_k128(sb);
-#pragma unroll
-          for (int k = 0; k < BK / 16; k++) umma_f16(d_tmem, desc_advance(da, k * 32), desc_advance(db, k * 32), idesc, (kb | k) != 0);
-          umma_commit(&empty[stage]);                 // stage reusable once these MMAs have read it
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
-        }
-        if (!ok) break;
-        umma_commit(&tmem_full[acc]);                 // accumulator complete
-      }
-    }
-  } else {
-    // ------------------------------------------------------------ epilogue (4 warps = 128 TMEM lanes)
-    const int quarter = warp & 3;                     // TMEM lane quarter this warp may access
-    int local = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, local++) {
-      const int m_blk = tile % num_m, n_blk = tile / num_m;
-      const int acc = local & 1; const uint32_t acc_phase = (local >> 1) & 1;
-      if (!mbar_wait(&tmem_full[acc], acc_phase, &s_abort, kWaitLimitNs)) { atomicExch(status, 4); break; }
-      tc_fence_after();
-      const int row = m_blk * BM + quarter * 32 + lane;
-      bf16* crow = C + (size_t)row * N + (size_t)n_blk * BN;
-      bf16* prow = C_pre ? C_pre + (size_t)row * N + (size_t)n_blk * BN : nullptr;
-      const bf16* brow = bias ? bias + (size_t)n_blk * BN : nullptr;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; c++) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + c * 32, r);
-        tmem_ld_wait();
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
-        if (brow) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 bb = *reinterpret_cast<const uint4*>(brow + c * 32 + i);
-            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bb);
-#pragma unroll
-            for (int j = 0; j < 4; j++) { float2 f = __bfloat1622float2(b2[j]); v[i + 2 * j] += f.x; v[i + 2 * j + 1] += f.y; }
-          }
-        }
-        if (prow) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 o; __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-            for (int j = 0; j < 4; j++) o2[j] = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
-            *reinterpret_cast<uint4*>(prow + c * 32 + i) = o;
-          }
-        }
-        if (act_gelu) {
-#pragma unroll
-          for (int i = 0; i < 32; i++) {
-            // activation of the value as stored (bf16), so that backward sees the same pre-activation
-            float x = prow ? __bfloat162float(__float2bfloat16_rn(v[i])) : v[i];
-            v[i] = gelu_tanh(x);
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          uint4 o; __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-          for (int j = 0; j < 4; j++) o2[j] = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
-          *reinterpret_cast<uint4*>(crow + c * 32 + i) = o;
-        }
-      }
-      tc_fence_before();
-      mbar_arrive(&tmem_empty[acc]);
-    }
-  }
-  // ---------------------------------------------------------------- teardown
-  tc_fence_before();
-  __syncthreads();
-  if (s_abort) {
-    // give copies that may still be in flight time to land before the shared memory is handed on
-    unsigned long long t0 = gtime_ns();
-    while (gtime_ns() - t0 < 2000000ull) __nanosleep(1000);
-    __syncthreads();
-  }
-  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+  if (threadIdx.x == 0) s_abort = 0;
+  if (threadIdx.x == 0) tma_prefetch_desc(&tmap_a);
+  PlainPolicy<BN> pol{&tmap_a, C, C_pre, bias, N, M / BM, N / BN, act_gelu};
+  gemm_persistent<BN, STAGES>(smem_raw, &tmap_b, pol, K, blockIdx.x, gridDim.x, status, &s_abort);
 }
 
 // ------------------------------------------------------------------ host
@@ -207,7 +102,7 @@ static int launch(const void* A, const void* B, void* C, void* C_pre, const void
   CUtensorMap ta, tb;
   if (!get_map(A, M, K, BM, &ta) || !get_map(B, N, K, BN, &tb)) return -3;
   static bool attr_set = false;
-  const int smem = L::TOTAL + 1024;
+  const int smem = L::DYNAMIC;
   if (!attr_set) {
     if (cudaFuncSetAttribute(gemm_bf16_nt_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
     attr_set = true;

@@ -10,6 +10,7 @@
 #include "comm.h"
 #include <cuda_runtime.h>
 #include <nvtx3/nvToolsExt.h>
+#include <algorithm>
 #include <chrono>
 #include <cstdarg>
 #include <cstdio>
@@ -85,7 +86,12 @@ int piccl_comm_create(int rank, int nranks, int device, const piccl_config_t* us
   RankCtx& x = c->h_ctx; memset(&x, 0, sizeof x);
   x.rank = rank; x.nranks = nranks; x.max_cta = cfg.max_cta; x.nslot = cfg.nslot; x.slot_bytes = cfg.slot_bytes;
   long long flags = round_up((long long)nranks * cfg.max_cta * kFlagStride, 4096);
-  x.tail_off = 0; x.head_off = flags; x.scratch_off = 2 * flags; x.scratch_bytes = round_up(cfg.scratch_bytes, 4096);
+  // low-latency slots: [parity][step][source rank], each 2 x the largest payload (line = 8 B data + 8 B flags)
+  long long ll_payload = (long long)e.ll_kb * 1024;
+  x.ll_slot_bytes = round_up(2 * ll_payload, 4096);
+  long long ll_bytes = ll_payload > 0 ? 2LL * kLLMaxSteps * nranks * x.ll_slot_bytes : 0;
+  x.tail_off = 0; x.head_off = flags; x.ll_off = 2 * flags; x.scratch_off = x.ll_off + ll_bytes; x.scratch_bytes = round_up(cfg.scratch_bytes, 4096);
+  c->ll_max_bytes = ll_payload;
   x.fifo_off = x.scratch_off + x.scratch_bytes;
   x.heap_bytes = x.fifo_off + (long long)nranks * cfg.max_cta * cfg.nslot * cfg.slot_bytes;
   c->heap_bytes = x.heap_bytes;
@@ -311,6 +317,50 @@ static int run(piccl_comm** comms, int n, const CallDesc* calls, cudaStream_t st
   const long long count = reducing ? (long long)d0.count : (long long)d0.count * esz_real;
   ExecKernelFn fn = reducing ? exec_kernel_for(d0.dtype, op) : exec_copy_kernel();
   if (!fn) return fail(PICCL_INTERNAL_ERROR, "no kernel for dtype %d op %d", d0.dtype, op);
+
+  // small exchange-type all-reduces take the low-latency kernel (flags travel inside the data lines)
+  if (d0.coll == COLL_ALLREDUCE && c0->ll_max_bytes > 0 && (long long)d0.count * esz_real <= c0->ll_max_bytes &&
+      (d0.algo == ALGO_RD || d0.algo == ALGO_RM || d0.algo == ALGO_PRD || d0.algo == ALGO_PRM)) {
+    Resolved rs = resolve(COLL_ALLREDUCE, d0.algo, d0.k, c0->nranks);
+    LLKernelFn lf = ll_kernel_for(d0.dtype, op);
+    if (rs.core == c0->nranks && !rs.radices.empty() && (int)rs.radices.size() <= kLLMaxSteps && rs.algo == d0.algo && lf) {
+      const bool permuted = d0.algo == ALGO_PRD || d0.algo == ALGO_PRM;
+      LLArgs la; memset(&la, 0, sizeof la);
+      la.n_vrank = n; la.nsteps = (int)rs.radices.size(); la.avg = avg ? 1 : 0; la.scale = avg ? 1.0f / (float)c0->nranks : 1.0f;
+      la.count = (long long)d0.count; la.timeout_ns = (unsigned long long)c0->cfg.timeout_ms * 1000000ull;
+      const int E = 8 / esz_real;
+      long long nlines = ((long long)d0.count + E - 1) / E;
+      la.n_cta = (int)((nlines + ll_lines_per_cta() - 1) / ll_lines_per_cta());
+      if (n * la.n_cta <= c0->sm_count) {
+        bool skip = false;
+        for (int i = 0; i < n; i++) {
+          piccl_comm* c = comms[i];
+          std::lock_guard<std::mutex> l(c->mu);
+          for (int s = 0; s < la.nsteps; s++) {
+            std::vector<int> pe = step_peers(c->rank, s, rs.radices, c->nranks, permuted);
+            std::sort(pe.begin(), pe.end());
+            la.npeers[s] = (uint8_t)pe.size();
+            int below = 0;
+            for (size_t j = 0; j < pe.size(); j++) { la.peers[i][s][j] = (uint8_t)pe[j]; if (pe[j] < c->rank) below++; }
+            la.self_pos[i][s] = (uint8_t)below;
+          }
+          la.r[i].ctx = c->d_ctx; la.r[i].in = calls[i].send; la.r[i].out = calls[i].recv;
+          la.epoch = ++c->ll_epoch;
+          c->stats.launches++; c->stats.calls[COLL_ALLREDUCE]++; c->stats.bytes[COLL_ALLREDUCE] += (unsigned long long)d0.count * esz_real;
+          skip |= fault_now(c); c->call_index++;
+        }
+        if (skip) return PICCL_OK;
+        nvtxRangePushA("allreduce_ll");
+        void* args[] = {&la};
+        cudaError_t e;
+        if (n > 1) e = cudaLaunchCooperativeKernel((const void*)lf, dim3(n * la.n_cta), dim3(kLLBlock), args, 0, stream);
+        else e = cudaLaunchKernel((const void*)lf, dim3(la.n_cta), dim3(kLLBlock), args, 0, stream);
+        nvtxRangePop();
+        if (e != cudaSuccess) return fail(PICCL_CUDA_ERROR, "low-latency launch failed: %s", cudaGetErrorString(e));
+        return PICCL_OK;
+      }
+    }
+  }
 
   // slabs: bound the local scratch of the recursive reduce-scatters
   long long slab = count, stride = 0;

@@ -36,6 +36,7 @@ static void load() {
   e.slot_kb = env_int("PICCL_SLOT_KB", 256);
   e.nslot = env_int("PICCL_NSLOT", 4);
   e.max_cta = env_int("PICCL_MAX_CTA", 32);
+  e.ll_kb = env_int("PICCL_LL_KB", 32);          // largest all-reduce taken by the low-latency kernel; 0 turns it off
   e.log_level = env_int("PICCL_LOG", 0);
   e.debug = env_int("PICCL_DEBUG", 0);
   const char* t = getenv("PICCL_TRACE"); e.trace_file = t ? t : "";

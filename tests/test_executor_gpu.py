@@ -192,12 +192,31 @@ def test_program_cache_and_stats(groups):
     outs = [torch.empty_like(x) for x in xs]
     before = g.stats(0)
     for _ in range(3):
-        g.run("allreduce", xs, outs, 4096, algo="PRD")
+        g.run("allreduce", xs, outs, 4096, algo="RING")      # FIFO path: compiled programs are cached
     _check_ok(g)
     after = g.stats(0)
     assert after.calls[1] - before.calls[1] == 3
     assert after.program_cache_hits - before.program_cache_hits >= 2
     assert after.launches - before.launches == 3
+
+
+def test_low_latency_path_matches_fifo_path(groups):
+    # small exchange-type all-reduces run the flag-in-data kernel, large ones the FIFO executor: same values
+    n = 8
+    g = groups(n)
+    for algo, k in [("PRD", 2), ("PRM", 8), ("RM", 4), ("RD", 2)]:
+        for dtype in (torch.float32, torch.bfloat16):
+            small = _inputs(n, 2000, dtype, seed=9)                       # 4-8 KB: low-latency kernel
+            outs = [torch.empty_like(x) for x in small]
+            before = g.stats(0).program_cache_misses + g.stats(0).program_cache_hits
+            g.run("allreduce", small, outs, 2000, algo=algo, k=k)
+            _check_ok(g)
+            assert g.stats(0).program_cache_misses + g.stats(0).program_cache_hits == before, "expected the low-latency kernel"
+            ref = _ref_reduce(small, "sum")
+            tol = _tol(dtype, n) * 4
+            for r in range(n):
+                assert torch.allclose(outs[r].float(), ref, atol=tol, rtol=tol), f"{algo} {dtype} rank {r}"
+                assert torch.equal(outs[r], outs[0])
 
 
 def test_bounded_wait_reports_instead_of_hanging():
