@@ -154,8 +154,7 @@ class GPT2:
             mean2, rstd2 = buf(("mean2", l), (T,), f32), buf(("rstd2", l), (T,), f32)
             ops.layernorm_fwd(a, xin, P("ln2_g"), P("ln2_b"), x2, ln2, mean2, rstd2, cfg.ln_eps)
             h, gl = buf(("h", l), (T, 4 * C)), buf(("g", l), (T, 4 * C))
-            gemm.linear(ln2, P("w_fc"), None, out=h)
-            ops.bias_gelu_fwd(h, P("b_fc"), h, gl)
+            gemm.linear_gelu(ln2, P("w_fc"), P("b_fc"), h, gl)
             pr = buf("pr", (T, C))
             gemm.linear(gl, P("w_proj"), P("b_proj"), out=pr)
             x3 = buf(("x3", l), (T, C))

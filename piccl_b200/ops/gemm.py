@@ -30,8 +30,10 @@ def counts() -> dict:
     return dict(_counts)
 
 
-def _own_kernel_ok(x, w, out) -> bool:
-    if _backend == "cublas":
+def _own_kernel_ok(x, w, out, fused_epilogue: bool = False) -> bool:
+    """"auto": the tcgen05 kernel where its fused epilogue saves a pass over the activations (bias + GELU);
+    plain products stay on cuBLAS, which is still a little faster on those shapes.  "tcgen05": wherever supported."""
+    if _backend == "cublas" or (_backend == "auto" and not fused_epilogue):
         return False
     from . import gemm_sm100
     return gemm_sm100.available() and gemm_sm100.supports(x, w, out)
@@ -48,6 +50,19 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias, out: torch.Tensor) -> torch.T
     if bias is None:
         return torch.mm(x, w.t(), out=out)
     return torch.addmm(bias, x, w.t(), out=out)
+
+
+def linear_gelu(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor, h_out: torch.Tensor, g_out: torch.Tensor) -> None:
+    """h_out = x @ w^T + bias;  g_out = gelu_tanh(h_out)   — one kernel where the tcgen05 GEMM is usable."""
+    if _own_kernel_ok(x, w, g_out, fused_epilogue=True):
+        from . import gemm_sm100
+        gemm_sm100.gemm_nt(x, w, g_out, bias=bias, gelu=True, pre=h_out)
+        _counts["tcgen05"] += 1
+        return
+    from . import bias_gelu_fwd
+    _counts["cublas"] += 1
+    torch.mm(x, w.t(), out=h_out)
+    bias_gelu_fwd(h_out, bias, h_out, g_out)
 
 
 def grad_input(dy: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:

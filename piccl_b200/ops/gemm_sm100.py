@@ -16,7 +16,7 @@ def available() -> bool:
     if _checked is None:
         try:
             lib = N.ops_lib()
-            _checked = hasattr(lib, "piccl_ops_gemm_bf16_nt") and torch.cuda.is_available() and torch.cuda.get_device_capability()[0] == 10
+            _checked = hasattr(lib, "piccl_ops_gemm_bf16_nt_ex") and torch.cuda.is_available() and torch.cuda.get_device_capability()[0] == 10
         except Exception:
             _checked = False
     return _checked
@@ -29,13 +29,14 @@ def supports(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
             and out.is_contiguous() and K % 64 == 0 and Nn % 128 == 0 and M % 128 == 0 and K >= 64)
 
 
-def gemm_nt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None, gelu: bool = False) -> torch.Tensor:
-    """out[M, N] = act(x[M, K] @ w[N, K]^T + bias)"""
+def gemm_nt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None, gelu: bool = False, pre=None) -> torch.Tensor:
+    """out[M, N] = act(x[M, K] @ w[N, K]^T + bias); `pre` (optional) receives the value before the activation"""
     M, K = x.shape
     Nn = w.shape[0]
-    rc = N.ops_lib().piccl_ops_gemm_bf16_nt(C.c_void_p(x.data_ptr()), C.c_void_p(w.data_ptr()), C.c_void_p(out.data_ptr()),
-                                            C.c_void_p(bias.data_ptr() if bias is not None else 0), M, Nn, K, int(gelu),
-                                            C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    rc = N.ops_lib().piccl_ops_gemm_bf16_nt_ex(C.c_void_p(x.data_ptr()), C.c_void_p(w.data_ptr()), C.c_void_p(out.data_ptr()),
+                                               C.c_void_p(pre.data_ptr() if pre is not None else 0),
+                                               C.c_void_p(bias.data_ptr() if bias is not None else 0), M, Nn, K, int(gelu),
+                                               C.c_void_p(torch.cuda.current_stream().cuda_stream))
     if rc != 0:
         raise RuntimeError(f"piccl_ops_gemm_bf16_nt failed (code {rc}) for M={M} N={Nn} K={K}")
     _bump()

@@ -40,8 +40,8 @@ def _algo(algo) -> int:
     return algo if isinstance(algo, int) else N.ALGO[algo.upper()]
 
 
-def make_config(max_cta=0, nslot=0, slot_bytes=0, scratch_bytes=0, block_size=0, timeout_ms=0) -> N.Config:
-    return N.Config(max_cta, nslot, slot_bytes, scratch_bytes, block_size, timeout_ms)
+def make_config(max_cta=0, nslot=0, slot_bytes=0, scratch_bytes=0, block_size=0, timeout_ms=0, tp_bytes=0) -> N.Config:
+    return N.Config(max_cta, nslot, slot_bytes, scratch_bytes, block_size, timeout_ms, tp_bytes)
 
 
 class _CommBase:

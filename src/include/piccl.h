@@ -29,12 +29,13 @@ enum { PICCL_OK = 0, PICCL_CUDA_ERROR = 1, PICCL_SYSTEM_ERROR = 2, PICCL_INTERNA
 
 /* ---- configuration ---- */
 typedef struct {
-  int max_cta;            /* FIFO channels (CTAs) per collective; 0: default 32 */
+  int max_cta;            /* FIFO channels (CTAs) per collective; 0: PICCL_MAX_CTA or 64 */
   int nslot;              /* FIFO depth per connection; 0: default 4 */
-  long long slot_bytes;   /* bytes per FIFO slot; 0: default 256 KiB */
+  long long slot_bytes;   /* bytes per FIFO slot; 0: PICCL_SLOT_KB or 512 KiB */
   long long scratch_bytes;/* local scratch for recursive reduce-scatter; 0: default 64 MiB */
   int block_size;         /* threads per CTA; 0: PICCL_BLOCK_SIZE or 512 */
-  int timeout_ms;         /* bound of every device-side wait; 0: PICCL_TIMEOUT_MS or 10000 */
+  int timeout_ms;         /* bound of every device-side wait; 0: PICCL_TIMEOUT_MS or 120000 */
+  long long tp_bytes;     /* workspace of the fused tensor-parallel kernels; 0: PICCL_TP_MB (default none) */
 } piccl_config_t;
 
 typedef struct piccl_comm piccl_comm_t;
@@ -84,6 +85,21 @@ int piccl_broadcast(piccl_comm_t* c, const void* send, void* recv, size_t count,
  * to exercise the multi-rank protocol on one GPU. */
 int piccl_group_collective(piccl_comm_t** comms, int ncomms, int coll, const void* const* send, void* const* recv,
                            size_t count, int dtype, int op, int root, int algo, int k, void* stream);
+
+/* ---- fused tensor-parallel kernels (tcgen05 GEMM + peer-memory collective in one kernel) ----
+ * All operands bf16, row-major, contiguous, 16-byte aligned.  The communicator needs tp_bytes >=
+ * piccl_tp_workspace_bytes(...).  M % (128 * nranks) == 0, N % 256 == 0 (N_local % 128), K % 64 == 0.
+ *
+ * piccl_gemm_rs:  out[M/n, N] = rows [rank*M/n, (rank+1)*M/n) of  sum_r A_r[M, K_local] * B_r[N, K_local]^T
+ * piccl_ag_gemm:  out[M, N_local] = concat_r(A_r[M/n, K]) * B[N_local, K]^T
+ * The *_group variants run several communicators of this process (virtual ranks on one device) as a
+ * single cooperative launch. */
+long long piccl_tp_workspace_bytes(int which /*0 gemm_rs, 1 ag_gemm*/, int nranks, int M, int N, int K);
+int piccl_gemm_rs(piccl_comm_t* c, const void* A, const void* B, void* out, int M, int N, int K_local, void* stream);
+int piccl_ag_gemm(piccl_comm_t* c, const void* A_shard, const void* B, void* out, int M, int N_local, int K, void* stream);
+int piccl_gemm_rs_group(piccl_comm_t** comms, int n, const void* const* A, const void* const* B, void* const* out, int M, int N, int K_local, void* stream);
+int piccl_ag_gemm_group(piccl_comm_t** comms, int n, const void* const* A_shard, const void* const* B, void* const* out, int M, int N_local, int K, void* stream);
+int piccl_tp_status(piccl_comm_t* c);   /* 0, or the role that gave up on a wait; synchronises */
 
 /* Test hook: launches the executor with one action that waits for data nobody
  * sends.  The wait runs into its time limit, the kernel returns and the status

@@ -29,6 +29,7 @@ struct RankCtx {
   long long tail_off, head_off, ll_off, scratch_off, fifo_off, heap_bytes;
   long long ll_slot_bytes;                // bytes of one low-latency slot (2 x the largest payload)
   long long scratch_bytes;
+  long long tp_flag_off, tp_data_off, tp_bytes;   // tensor-parallel workspace: epoch flags (1 MiB, zeroed) and payload
   char* heap[kMaxRanks];                  // every rank's heap as mapped in this process
   unsigned long long* sent;               // [nranks * max_cta] entries pushed per (peer, cta)
   unsigned long long* rcvd;               // [nranks * max_cta] entries consumed per (peer, cta)

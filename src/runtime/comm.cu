@@ -90,10 +90,16 @@ int piccl_comm_create(int rank, int nranks, int device, const piccl_config_t* us
   long long ll_payload = (long long)e.ll_kb * 1024;
   x.ll_slot_bytes = round_up(2 * ll_payload, 4096);
   long long ll_bytes = ll_payload > 0 ? 2LL * kLLMaxSteps * nranks * x.ll_slot_bytes : 0;
-  x.tail_off = 0; x.head_off = flags; x.ll_off = 2 * flags; x.scratch_off = x.ll_off + ll_bytes; x.scratch_bytes = round_up(cfg.scratch_bytes, 4096);
+  if (cfg.tp_bytes <= 0) cfg.tp_bytes = (long long)e.tp_mb << 20;
+  c->cfg.tp_bytes = cfg.tp_bytes;
+  const long long tp_flags = cfg.tp_bytes > 0 ? (1 << 20) : 0;
+  x.tail_off = 0; x.head_off = flags; x.ll_off = 2 * flags; x.tp_flag_off = x.ll_off + ll_bytes;
+  x.scratch_off = x.tp_flag_off + tp_flags; x.scratch_bytes = round_up(cfg.scratch_bytes, 4096);
   c->ll_max_bytes = ll_payload;
   x.fifo_off = x.scratch_off + x.scratch_bytes;
-  x.heap_bytes = x.fifo_off + (long long)nranks * cfg.max_cta * cfg.nslot * cfg.slot_bytes;
+  x.tp_data_off = round_up(x.fifo_off + (long long)nranks * cfg.max_cta * cfg.nslot * cfg.slot_bytes, 4096);
+  x.tp_bytes = round_up(cfg.tp_bytes, 4096);
+  x.heap_bytes = x.tp_data_off + x.tp_bytes;
   c->heap_bytes = x.heap_bytes;
 
   cudaError_t err;
@@ -181,6 +187,7 @@ int piccl_comm_destroy(piccl_comm_t* c) {
   for (auto& ch : c->chunks) { cudaFree(ch.dev); cudaFreeHost(ch.host); }
   for (auto& kv : c->cache) if (kv.second.ready) cudaEventDestroy(kv.second.ready);
   for (auto& t : c->trace) { if (t.start) cudaEventDestroy(t.start); if (t.stop) cudaEventDestroy(t.stop); }
+  if (c->d_tp_status) cudaFree(c->d_tp_status);
   cudaFree(c->heap); cudaFree(c->d_sent); cudaFree(c->d_rcvd); cudaFree(c->d_abort); cudaFree(c->d_ctx);
   if (c->h_status) cudaFreeHost(c->h_status);
   cudaGetLastError();

@@ -54,6 +54,8 @@ struct piccl_comm {
   bool ipc_opened[piccl::kMaxRanks] = {false};
   bool connected = false, broken = false;
   unsigned long long call_index = 0;
+  unsigned tp_epoch_rs = 0, tp_epoch_ag = 0;   // epochs of the fused tensor-parallel kernels
+  int* d_tp_status = nullptr;
   unsigned ll_epoch = 0;               // epoch of the last low-latency all-reduce (same on all ranks)
   long long ll_max_bytes = 0;          // largest message the low-latency path takes (0: off)
   piccl_stats_t stats{};

@@ -33,10 +33,12 @@ static void load() {
   e.min_grid = env_int("PICCL_MIN_GRID_SIZE", 1, &e.min_grid_set);
   e.timeout_ms = env_int("PICCL_TIMEOUT_MS", 120000);
   e.scratch_mb = env_int("PICCL_SCRATCH_MB", 64);
-  e.slot_kb = env_int("PICCL_SLOT_KB", 256);
+  e.slot_kb = env_int("PICCL_SLOT_KB", 512);
   e.nslot = env_int("PICCL_NSLOT", 4);
-  e.max_cta = env_int("PICCL_MAX_CTA", 32);
-  e.ll_kb = env_int("PICCL_LL_KB", 32);          // largest all-reduce taken by the low-latency kernel; 0 turns it off
+  e.max_cta = env_int("PICCL_MAX_CTA", 64);
+  e.ll_kb = env_int("PICCL_LL_KB", 128);         // largest all-reduce taken by the low-latency kernel; 0 turns it off
+  e.tp_mb = env_int("PICCL_TP_MB", 0);           // heap space for the fused tensor-parallel kernels (0: none)
+  e.tp_feeders = env_int("PICCL_TP_FEEDERS", 24); // CTAs that push the local shard in all-gather -> GEMM
   e.log_level = env_int("PICCL_LOG", 0);
   e.debug = env_int("PICCL_DEBUG", 0);
   const char* t = getenv("PICCL_TRACE"); e.trace_file = t ? t : "";
