@@ -1,0 +1,52 @@
+#!/bin/bash
+# Collective sweeps for the baseline table: this library, stock NCCL and the reference build, same harness
+# (coll_bench), only LD_PRELOAD and the PICCL_* variables change.
+#   benchmarks/run_sweeps.sh N OUTDIR [quick]
+# Writes OUTDIR/sweep_<N>.csv (all rows) .  Reference rows are only produced for configurations in which the
+# reference is valid (fp32/int32, allreduce all algorithms, allgather RING/K_RING/PRD/PRM with k a power that
+# fits, reduce RING, broadcast RING/K_RING in place); its stubs and unsafe configurations are not run.
+N=${1:-2}; OUT=${2:-gpurun_out}; QUICK=${3:-}
+HERE="$(cd "$(dirname "$0")/.." && pwd)"; cd "$HERE"
+CB=piccl_b200/lib/coll_bench; OURS=piccl_b200/lib/piccl.so; REF=baseline/_ref/piccl.so
+mkdir -p "$OUT"; CSV="$OUT/sweep_$N.csv"; : > "$CSV"
+IS=1000; IL=100; [ -n "$QUICK" ] && { IS=200; IL=20; }
+run() {  # label preload coll algo k dtype min max extra...
+  local label=$1 pre=$2 coll=$3 algo=$4 k=$5 dt=$6 min=$7 max=$8; shift 8
+  local up; up=$(echo "$coll" | tr a-z A-Z)
+  env ${pre:+LD_PRELOAD=$pre} ${algo:+PICCL_${up}_ALGO=$algo} ${k:+PICCL_${up}_K=$k} timeout 300 $CB --gpus $N --coll $coll --dtype $dt --min $min --max $max \
+      --check --label "$label" --iters-small $IS --iters-large $IL "$@" 2>/dev/null | grep -v "^#\|^\[PICCL\|NCCL version\|PICCL_" >> "$CSV"
+}
+KS="2 4"; [ "$N" -ge 8 ] && KS="2 4 8"
+AR_MAX=1073741824; BLK_MAX=268435456; [ -n "$QUICK" ] && { AR_MAX=268435456; BLK_MAX=67108864; }
+# ---- allreduce, fp32 and bf16
+for dt in float bf16; do
+  run nccl "" allreduce "" "" $dt 8 $AR_MAX
+  run ours-RING-k-1 $OURS allreduce RING "" $dt 8 $AR_MAX
+  run ours-PRD-k-1 $OURS allreduce PRD "" $dt 8 $AR_MAX
+  for k in $KS; do run ours-PRM-k$k $OURS allreduce PRM $k $dt 8 $AR_MAX; done
+  for k in 2 4; do [ $((N % k)) -eq 0 ] && [ $k -lt $N ] && run ours-K_RING-k$k $OURS allreduce K_RING $k $dt 8 $AR_MAX; done
+done
+if [ -f $REF ]; then
+  run ref-RING $REF allreduce RING "" float 8 $AR_MAX
+  run ref-PRD $REF allreduce PRD "" float 8 $AR_MAX
+  for k in $KS; do run ref-PRM-k$k $REF allreduce PRM $k float 8 $AR_MAX; done
+  for k in 2 4; do [ $((N % k)) -eq 0 ] && [ $k -lt $N ] && run ref-K_RING-k$k $REF allreduce K_RING $k float 8 $AR_MAX; done
+fi
+# ---- the other collectives (per-rank block sizes)
+for coll in allgather reduce_scatter reduce broadcast; do
+  for dt in float bf16; do
+    run nccl "" $coll "" "" $dt 1024 $BLK_MAX
+    run ours-RING-k-1 $OURS $coll RING "" $dt 1024 $BLK_MAX
+    run ours-PRD-k-1 $OURS $coll PRD "" $dt 1024 $BLK_MAX
+    run ours-PRM-k2 $OURS $coll PRM 2 $dt 1024 $BLK_MAX
+    [ $((N % 2)) -eq 0 ] && [ 2 -lt $N ] && run ours-K_RING-k2 $OURS $coll K_RING 2 $dt 1024 $BLK_MAX
+  done
+done
+if [ -f $REF ]; then
+  run ref-RING $REF allgather RING "" float 1024 $BLK_MAX
+  run ref-PRD $REF allgather PRD "" float 1024 $BLK_MAX
+  run ref-PRM-k2 $REF allgather PRM 2 float 1024 $BLK_MAX
+  run ref-RING $REF reduce RING "" float 1024 $BLK_MAX
+  run ref-RING $REF broadcast RING "" float 1024 $BLK_MAX --in-place
+fi
+echo "rows: $(wc -l < "$CSV")"

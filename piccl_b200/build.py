@@ -4,6 +4,7 @@
   piccl_b200/lib/libpiccl_ops.so model kernels (tcgen05 GEMM, layer norm, cross entropy, AdamW, ...)
   piccl_b200/lib/piccl_sched     schedule dump / validation command line tool
   piccl_b200/lib/coll_bench      OSU-style collective benchmark (fork per GPU, no MPI)
+  piccl_b200/lib/loggp_bench     PRTT measurements between two GPUs (input of tools/loggp_param)
 
 The reference builds one piccl.so with a single nvcc call and no arch flag
 (src/Makefile:7-17); here every translation unit is compiled separately (in
@@ -52,6 +53,10 @@ def targets() -> dict[str, dict]:
         "piccl_sched": {
             "src": _sources("coll/*.cc", "tools/piccl_sched.cc"),
             "link": [],
+        },
+        "loggp_bench": {
+            "src": [ROOT / "tools" / "loggp_bench" / "loggp_bench.cu"],
+            "link": ["-cudart", "static", "-ldl", "-lpthread", "-lrt"],
         },
         "coll_bench": {
             "src": [ROOT / "benchmarks" / "coll_bench.cc"],

@@ -185,9 +185,45 @@ def case_fault(rank, world):
     comm.close()
 
 
+def case_tp(rank, world):
+    """Fused GEMM->reduce-scatter and all-gather->GEMM across real GPUs against cuBLAS + NCCL."""
+    from piccl_b200.parallel import tp
+    from piccl_b200.parallel.comm import Communicator, make_config
+    M, N, K = 256 * world * 2, 1024, 512
+    ws = max(tp.workspace_bytes("gemm_rs", world, M, N, K), tp.workspace_bytes("ag_gemm", world, M, N, K))
+    comm = Communicator(config=make_config(tp_bytes=ws, timeout_ms=20000))
+    g = torch.Generator(device="cuda").manual_seed(50 + rank)
+    A = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    B = (torch.randn(N, K, generator=g, device="cuda") * 0.1).to(torch.bfloat16)
+    out = torch.empty(M // world, N, device="cuda", dtype=torch.bfloat16)
+    for _ in range(3):
+        tp.gemm_rs(comm, A, B, out)
+    torch.cuda.synchronize()
+    assert tp.tp_status(comm) == 0
+    part = (A @ B.t())
+    ref = torch.empty_like(out)
+    dist.reduce_scatter_tensor(ref, part)
+    tol = 0.03 * ref.float().abs().max().item() + 0.05
+    assert torch.allclose(out.float(), ref.float(), atol=tol, rtol=3e-2), (out.float() - ref.float()).abs().max().item()
+    # all-gather -> GEMM
+    As = torch.randn(M // world, K, generator=g, device="cuda").to(torch.bfloat16)
+    out2 = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    for _ in range(3):
+        tp.ag_gemm(comm, As, B, out2)
+    torch.cuda.synchronize()
+    assert tp.tp_status(comm) == 0
+    full = torch.empty(M, K, device="cuda", dtype=torch.bfloat16)
+    dist.all_gather_into_tensor(full, As)
+    ref2 = full @ B.t()
+    tol = 0.03 * ref2.float().abs().max().item() + 0.05
+    assert torch.allclose(out2.float(), ref2.float(), atol=tol, rtol=3e-2), (out2.float() - ref2.float()).abs().max().item()
+    dist.barrier()
+    comm.close()
+
+
 if __name__ == "__main__":
     case = sys.argv[1]
     rank, world = setup()
-    {"collectives": case_collectives, "ddp": case_ddp, "shim": case_shim, "fault": case_fault}[case](rank, world)
+    {"collectives": case_collectives, "ddp": case_ddp, "shim": case_shim, "fault": case_fault, "tp": case_tp}[case](rank, world)
     print(f"WORKER_OK {case} rank {rank}", flush=True)
     dist.destroy_process_group()

@@ -43,6 +43,10 @@ def test_data_parallel_training():
     _run("ddp")
 
 
+def test_fused_tensor_parallel_kernels():
+    _run("tp")
+
+
 def test_preload_shim_under_torch_distributed():
     from piccl_b200 import build
     so = str(build.lib_path("piccl.so"))
