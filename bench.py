@@ -35,7 +35,9 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="piccl", choices=["piccl", "reference"])
+    ap.add_argument("--impl", default="piccl", choices=["piccl", "reference", "ddp"],
+                    help="piccl: this framework's trainer; reference: stock PyTorch DDP under the reference .so; ddp: stock PyTorch DDP under --preload")
+    ap.add_argument("--preload", default="", help="with --impl ddp: library to LD_PRELOAD (e.g. piccl_b200/lib/piccl.so; PICCL_*_ALGO from the environment); empty: none")
     ap.add_argument("--model", default="medium", choices=["medium", "tiny"])
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--algo", default=None, help="all-reduce algorithm of the bucket reductions (RING, K_RING, RD, RM, PRD, PRM, AUTO)")
@@ -214,6 +216,17 @@ def ensure_reference():
     return None
 
 
+def reexec_under(preload: str):
+    """Re-executes this process with `preload` in LD_PRELOAD (nothing if empty): the drop-in configuration, stock PyTorch DDP
+    whose NCCL calls the preloaded library intercepts."""
+    env = dict(os.environ)
+    if preload:
+        env["LD_PRELOAD"] = str(Path(preload).resolve())
+    env["PICCL_BENCH_UNDER_REFERENCE"] = "1"
+    env["PICCL_BENCH_LABEL"] = f"ddp:{preload or 'none'}"
+    os.execve(sys.executable, [sys.executable] + sys.argv, env)
+
+
 def reexec_under_reference():
     """Re-executes this process with the reference .so preloaded.  The reference opens "libnccl.so" in a
     constructor (src/piccl.c:206-211), so a directory whose libnccl.so / libnccl.so.2 point at the NCCL
@@ -244,6 +257,8 @@ def reexec_under_reference():
 def run_reference(args):
     rank, world, local = dist_env()
     if os.environ.get("PICCL_BENCH_UNDER_REFERENCE") != "1":
+        if args.impl == "ddp":
+            reexec_under(args.preload)
         why = ensure_reference()
         if why is None:
             why = reexec_under_reference()      # only returns on failure
@@ -299,12 +314,14 @@ def run_reference(args):
     clocks = sampler.stop() if sampler else None
     if rank == 0:
         print(json.dumps({
-            "impl": "reference", "metric": "DDP GPT-2 medium training throughput" if args.model == "medium" else "DDP GPT-2 tiny training throughput",
+            "impl": os.environ.get("PICCL_BENCH_LABEL", "reference"), "metric": "DDP GPT-2 medium training throughput" if args.model == "medium" else "DDP GPT-2 tiny training throughput",
             "value": round(tokens_per_step / ms_dev * 1e3, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms_dev, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic: token ids uniform over the vocabulary, random-init weights",
             "config": {"model": f"gpt2-{args.model}", "global_batch": world * args.micro_batch, "seq_len": cfg.seq_len, "parallelism": f"dp{world}", "bucket_mb": 25,
-                       "stack": "unmodified reference piccl.so preloaded (algorithms unset: its bf16-capable path is the NCCL passthrough) under stock PyTorch DDP + fused AdamW",
+                       "stack": ("stock PyTorch DDP + fused AdamW under LD_PRELOAD given below" if args.impl == "ddp" else
+                                 "unmodified reference piccl.so preloaded (algorithms unset: its bf16-capable path is the NCCL passthrough) under stock PyTorch DDP + fused AdamW"),
+                       "allreduce_algo_env": os.environ.get("PICCL_ALLREDUCE_ALGO", ""),
                        "preload": os.environ.get("LD_PRELOAD", "")},
             "e2e": {"value": round(tokens_per_step / ms_e2e * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 3), "wall_ms_per_step": round(wall_e2e, 3),
                     "h2d_bytes_per_step": 2 * args.micro_batch * cfg.seq_len * 8, "d2h_bytes_per_step": 4, "last_loss": last_loss},
@@ -317,4 +334,4 @@ def run_reference(args):
 
 if __name__ == "__main__":
     a = parse()
-    sys.exit(run_reference(a) if a.impl == "reference" else run_piccl(a))
+    sys.exit(run_reference(a) if a.impl in ("reference", "ddp") else run_piccl(a))

@@ -12,7 +12,7 @@
 //   coll_bench --gpus 8 --coll allreduce --dtype float --min 8 --max 1073741824 --check
 //
 // Sizes: --min/--max are bytes of the whole buffer for allreduce/broadcast/reduce and bytes
-// per rank for allgather/reduce_scatter; powers of two in between.
+// per rank for allgather/reduce_scatter; powers of two in between (--step 4: every second one).
 // Output: one CSV line per size on stdout (rank 0).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -60,7 +60,7 @@ enum CollKind { AR, AG, RS, RD, BC };
 struct Opt {
   int gpus = 2; CollKind coll = AR; std::string coll_name = "allreduce"; ncclDataType_t dt = ncclFloat; std::string dt_name = "float";
   ncclRedOp_t op = ncclSum; std::string op_name = "sum"; size_t minb = 8, maxb = 1 << 26; int root = 0; bool check = false, in_place = false;
-  int iters_small = 1000, iters_large = 100, warmup = 5; size_t large = 1000000; std::string label = "";
+  int iters_small = 1000, iters_large = 100, warmup = 5, step = 2; size_t large = 1000000; std::string label = "";
 };
 
 static size_t dt_size(ncclDataType_t d) { switch (d) { case ncclFloat: return 4; case ncclInt32: return 4; case ncclBfloat16: return 2; case ncclHalf: return 2; case ncclDouble: return 8; default: return 1; } }
@@ -129,7 +129,7 @@ static int run_rank(const Opt& o, int rank, Shared* sh) {
   CK(cudaMemset(sbuf, 0, big * es)); CK(cudaMemset(rbuf, 0, big * es));
   if (rank == 0) printf("# coll,label,dtype,op,ranks,bytes,iters,time_us,algbw_GBs,busbw_GBs,check\n");
 
-  for (size_t bytes = o.minb; bytes <= o.maxb; bytes *= 2) {
+  for (size_t bytes = o.minb; bytes <= o.maxb; bytes *= o.step) {
     size_t count = bytes / es; if (count == 0) count = 1;
     size_t send_count = (o.coll == RS) ? count * n : count, recv_count = (o.coll == AG) ? count * n : count;
     const void* send = sbuf; void* recv = rbuf;
@@ -150,6 +150,7 @@ static int run_rank(const Opt& o, int rank, Shared* sh) {
       fill_host(h, o.dt, rank, send_count);
       CK(cudaMemcpy(sbuf, h.data(), send_count * es, cudaMemcpyHostToDevice));
       CK(cudaMemset(rbuf, 0xff, recv_count * es));
+      CK(cudaDeviceSynchronize());      // the fill runs on the legacy stream, the collective on a non-blocking one
       call(); CK(cudaStreamSynchronize(st));
       std::vector<unsigned char> out(recv_count * es);
       CK(cudaMemcpy(out.data(), rbuf, recv_count * es, cudaMemcpyDeviceToHost));
@@ -219,6 +220,7 @@ int main(int argc, char** argv) {
     else if (f == "--iters-large") o.iters_large = atoi(val().c_str());
     else if (f == "--warmup") o.warmup = atoi(val().c_str());
     else if (f == "--label") o.label = val();
+    else if (f == "--step") { o.step = atoi(val().c_str()); if (o.step < 2) o.step = 2; }
     else { fprintf(stderr, "unknown flag %s\n", f.c_str()); return 2; }
   }
   if (o.gpus < 1 || o.gpus > 64 || o.minb < 1 || o.maxb < o.minb) { fprintf(stderr, "bad arguments\n"); return 2; }

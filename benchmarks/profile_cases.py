@@ -1,0 +1,89 @@
+"""Small, self-terminating workloads for ncu captures (one kernel, a few launches, well under a few GB):
+
+    python benchmarks/profile_cases.py exec      # fused collective executor: 2 virtual ranks, ring all-reduce of 256 MiB fp32
+    python benchmarks/profile_cases.py exec_ll   # low-latency all-reduce, 8 virtual ranks, 16 KiB
+    python benchmarks/profile_cases.py gemm      # tcgen05 GEMM 8192 x 8192 x 3584 bf16
+    python benchmarks/profile_cases.py tp        # fused GEMM -> reduce-scatter, 2 virtual ranks, 4096 x 4096 x 2048
+    python benchmarks/profile_cases.py ln        # residual-add + LayerNorm forward/backward, 8192 x 1024
+    python benchmarks/profile_cases.py ce        # cross entropy forward+backward, 8192 x 50304
+
+Typical capture (after the same command has exited 0 without ncu):
+    ncu --set full --clock-control none -k regex:<kernel> -s 2 -c 2 -o gpurun_out/<name> python benchmarks/profile_cases.py <case>
+"""
+from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+import torch
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
+
+def case_exec(ll: bool = False):
+    from piccl_b200.parallel.comm import LoopbackGroup
+    n = 8 if ll else 2
+    count = 4096 if ll else 64 << 20
+    g = LoopbackGroup(n)
+    xs = [torch.ones(count, device="cuda") for _ in range(n)]
+    outs = [torch.empty_like(x) for x in xs]
+    for _ in range(4):
+        g.run("allreduce", xs, outs, count, algo="PRD" if ll else "RING")
+    torch.cuda.synchronize()
+    assert g.status().aborted == 0
+    g.close()
+
+
+def case_gemm():
+    from piccl_b200.ops import gemm_sm100
+    a = torch.randn(8192, 3584, device="cuda").to(torch.bfloat16)
+    b = torch.randn(8192, 3584, device="cuda").to(torch.bfloat16)
+    o = torch.empty(8192, 8192, device="cuda", dtype=torch.bfloat16)
+    for _ in range(4):
+        gemm_sm100.gemm_nt(a, b, o)
+    torch.cuda.synchronize()
+
+
+def case_tp():
+    from piccl_b200.parallel import tp
+    from piccl_b200.parallel.comm import LoopbackGroup, make_config
+    n, M, N, K = 2, 4096, 4096, 2048
+    g = LoopbackGroup(n, config=make_config(tp_bytes=tp.workspace_bytes("gemm_rs", n, M, N, K)))
+    As = [torch.randn(M, K, device="cuda").to(torch.bfloat16) for _ in range(n)]
+    Bs = [torch.randn(N, K, device="cuda").to(torch.bfloat16) for _ in range(n)]
+    outs = [torch.empty(M // n, N, device="cuda", dtype=torch.bfloat16) for _ in range(n)]
+    for _ in range(4):
+        tp.gemm_rs_group(g, As, Bs, outs)
+    torch.cuda.synchronize()
+    g.close()
+
+
+def case_ln():
+    from piccl_b200 import ops
+    T, C = 8192 * 4, 1024
+    x, r = torch.randn(T, C, device="cuda").bfloat16(), torch.randn(T, C, device="cuda").bfloat16()
+    g_, b_ = torch.ones(C, device="cuda").bfloat16(), torch.zeros(C, device="cuda").bfloat16()
+    s, y = torch.empty_like(x), torch.empty_like(x)
+    mean, rstd = torch.empty(T, device="cuda"), torch.empty(T, device="cuda")
+    dx, dg, db = torch.empty_like(x), torch.empty_like(g_), torch.empty_like(b_)
+    for _ in range(4):
+        ops.layernorm_fwd(x, r, g_, b_, s, y, mean, rstd)
+        ops.layernorm_bwd(y, s, g_, mean, rstd, r, dx, dg, db)
+    torch.cuda.synchronize()
+
+
+def case_ce():
+    from piccl_b200 import ops
+    T, V, Vp = 8192, 50257, 50304
+    logits = torch.randn(T, Vp, device="cuda").bfloat16()
+    tgt = torch.randint(0, V, (T,), device="cuda")
+    loss = torch.empty(T, device="cuda")
+    for _ in range(4):
+        ops.cross_entropy_fwd_bwd(logits, tgt, loss, V, 1.0 / T)
+    torch.cuda.synchronize()
+
+
+if __name__ == "__main__":
+    which = sys.argv[1] if len(sys.argv) > 1 else "exec"
+    {"exec": case_exec, "exec_ll": lambda: case_exec(True), "gemm": case_gemm, "tp": case_tp, "ln": case_ln, "ce": case_ce}[which]()
+    print(f"profile case {which} done")

@@ -35,7 +35,7 @@ class Status(C.Structure):
 class Stats(C.Structure):
     _fields_ = [("calls", C.c_ulonglong * 5), ("bytes", C.c_ulonglong * 5), ("launches", C.c_ulonglong),
                 ("program_cache_hits", C.c_ulonglong), ("program_cache_misses", C.c_ulonglong),
-                ("fallbacks", C.c_ulonglong), ("timeouts", C.c_ulonglong)]
+                ("fallbacks", C.c_ulonglong), ("timeouts", C.c_ulonglong), ("persistent_calls", C.c_ulonglong)]
 
 
 def _ensure_built(name: str) -> Path:

@@ -57,6 +57,7 @@ typedef struct {
   unsigned long long program_cache_hits, program_cache_misses;
   unsigned long long fallbacks;     /* calls the executor declined (reason logged with PICCL_LOG>=1) */
   unsigned long long timeouts;
+  unsigned long long persistent_calls; /* calls served by the persistent launcher instead of a kernel launch */
 } piccl_stats_t;
 
 /* ---- communicator life cycle ----

@@ -18,6 +18,7 @@
 //     bool tile_begin(int m_blk, int n_blk, int et, volatile int* abort);   // epilogue threads (et 0..127), before the stores
 //     void store(int m_blk, int n_blk, int row, int col0, float (&v)[32]);  // 32 consecutive columns of one row
 //     void tile_end(int m_blk, int n_blk, int et);                   // after all 128 epilogue threads stored (barrier done)
+//     static constexpr int STAGING; void set_staging(uint8_t*);      // bytes of shared memory the epilogue wants, and where they are
 //   };
 // Every wait is bounded; see gemm_persistent for the abort protocol.
 #pragma once
@@ -28,11 +29,12 @@ namespace sm100 {
 constexpr int GEMM_BM = 128, GEMM_BK = 64, GEMM_THREADS = 192;
 constexpr unsigned long long kGemmWaitLimitNs = 4000000000ull;   // 4 s
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int STAGING = 0>
 struct GemmSmem {
   static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2, B_BYTES = BN * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int BAR_OFF = STAGES * STAGE_BYTES;
+  static constexpr int STAGING_OFF = STAGES * STAGE_BYTES;          // epilogue staging tile (policies that store through shared memory)
+  static constexpr int BAR_OFF = STAGING_OFF + STAGING;
   static constexpr int TOTAL = BAR_OFF + (2 * STAGES + 4) * 8 + 16;
   static constexpr int DYNAMIC = TOTAL + 1024;          // slack for the 1024-byte alignment of the tiles
 };
@@ -46,8 +48,9 @@ __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 1
 template <int BN, int STAGES, class Policy>
 __device__ __forceinline__ void gemm_persistent(uint8_t* smem_raw, const CUtensorMap* tmap_b, Policy& pol, int K, int first_tile, int tile_stride,
                                                 int* status, volatile int* s_abort) {
-  typedef GemmSmem<BN, STAGES> L;
+  typedef GemmSmem<BN, STAGES, Policy::STAGING> L;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  pol.set_staging(smem + L::STAGING_OFF);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* empty = full + STAGES;
   uint64_t* tmem_full = empty + STAGES;

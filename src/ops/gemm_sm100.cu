@@ -39,6 +39,8 @@ struct PlainPolicy {
   __device__ void tile(int idx, int& m_blk, int& n_blk) const { m_blk = idx % num_m; n_blk = idx / num_m; }
   __device__ const CUtensorMap* a_map(int m_blk, int& row0) const { row0 = m_blk * BM; return ta; }
   __device__ bool gate(int, volatile int*) const { return true; }
+  static constexpr int STAGING = 0;
+  __device__ void set_staging(uint8_t*) {}
   __device__ bool tile_begin(int, int, int, volatile int*) { return true; }
   __device__ void tile_end(int, int, int) {}
   __device__ void store(int m_blk, int n_blk, int row, int col0, float (&v)[32]) {

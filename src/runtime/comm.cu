@@ -177,6 +177,7 @@ int piccl_comm_destroy(piccl_comm_t* c) {
   if (!c) return PICCL_OK;
   DevGuard g(c->device);
   cudaDeviceSynchronize();
+  persist_destroy(c);
   if (!env().trace_file.empty()) trace_dump(c);
   if (env().log_level >= 1) {
     const piccl_stats_t& s = c->stats;
@@ -246,12 +247,36 @@ static int upload_program(piccl_comm* c, const Program& p, cudaStream_t stream, 
   return PICCL_OK;
 }
 
+// PICCL_DEBUG=1: every action of a freshly compiled program is checked against the extents of the
+// buffers of the call before it is ever given to the device (ranges, peers, scratch capacity).
+static const char* check_program(const Program& p, const CollArgs& a, long long scratch_cap_elems) {
+  const long long st = a.block_stride ? a.block_stride : a.count;
+  long long in_elems = a.count, out_elems = a.count;
+  if (a.coll == COLL_ALLGATHER) out_elems = (a.nranks - 1) * st + a.count;
+  if (a.coll == COLL_REDUCE_SCATTER) in_elems = (a.nranks - 1) * st + a.count;
+  for (const Action& ac : p.actions) {
+    if (ac.count <= 0 || ac.n_recv > kMaxActionPeers || ac.n_send > kMaxActionPeers) return "bad operand count";
+    for (int i = 0; i < ac.n_recv; i++) if (ac.recv_peer[i] >= a.nranks || ac.recv_peer[i] == p.rank) return "bad receive peer";
+    for (int i = 0; i < ac.n_send; i++) if (ac.send_peer[i] >= a.nranks || ac.send_peer[i] == p.rank) return "bad send peer";
+    const long long slim = ac.src_buf == BUF_IN ? in_elems : ac.src_buf == BUF_OUT ? out_elems : scratch_cap_elems;
+    if (ac.src_buf != BUF_NONE && (ac.src_off < 0 || ac.src_off + ac.count > slim)) return "source range outside its buffer";
+    const long long dlim = ac.dst_buf == BUF_OUT ? out_elems : scratch_cap_elems;
+    if (ac.dst_buf == BUF_IN) return "write to the send buffer";
+    if (ac.dst_buf != BUF_NONE && (ac.dst_off < 0 || ac.dst_off + ac.count > dlim)) return "destination range outside its buffer";
+  }
+  return nullptr;
+}
+
 static int get_program(piccl_comm* c, const CollArgs& a, cudaStream_t stream, const ProgEntry** out) {
   ProgKey k{(int)a.coll, (int)a.algo, a.k, a.root, a.elem_size, a.in_place ? 1 : 0, a.count, a.block_stride};
   auto it = c->cache.find(k);
   if (it == c->cache.end()) {
     c->stats.program_cache_misses++;
     Program p = compile(a, c->rank);
+    if (env().debug) {
+      if (const char* why = check_program(p, a, c->h_ctx.scratch_bytes / std::max(1, a.elem_size)))
+        return fail(PICCL_INTERNAL_ERROR, "program check failed (%s %s, rank %d): %s", coll_name(a.coll), algo_name(a.algo), c->rank, why);
+    }
     ProgEntry e;
     int rc = upload_program(c, p, stream, e); if (rc) return rc;
     it = c->cache.emplace(k, e).first;
@@ -357,6 +382,11 @@ static int run(piccl_comm** comms, int n, const CallDesc* calls, cudaStream_t st
           skip |= fault_now(c); c->call_index++;
         }
         if (skip) return PICCL_OK;
+        if (env().launch_persistent) {
+          const void* ins[kMaxVRanks]; void* outs[kMaxVRanks];
+          for (int i = 0; i < n; i++) { ins[i] = calls[i].send; outs[i] = calls[i].recv; }
+          if (persist_allreduce(comms, n, la, ins, outs, (long long)d0.count, d0.dtype, op, avg ? 1 : 0, (int)d0.algo, d0.k, stream) == PICCL_OK) { c0->stats.persistent_calls++; return PICCL_OK; }
+        }
         nvtxRangePushA("allreduce_ll");
         void* args[] = {&la};
         cudaError_t e;

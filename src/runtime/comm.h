@@ -56,6 +56,7 @@ struct piccl_comm {
   unsigned long long call_index = 0;
   unsigned tp_epoch_rs = 0, tp_epoch_ag = 0;   // epochs of the fused tensor-parallel kernels
   int* d_tp_status = nullptr;
+  void* persist = nullptr;             // state of the persistent launcher (runtime/persistent.cu)
   unsigned ll_epoch = 0;               // epoch of the last low-latency all-reduce (same on all ranks)
   long long ll_max_bytes = 0;          // largest message the low-latency path takes (0: off)
   piccl_stats_t stats{};
@@ -73,4 +74,8 @@ void trace_dump(piccl_comm* c);
 // Algorithm choice for AUTO / unspecified requests: PICCL_TUNE_FILE table if given, else built-in thresholds.
 Algo select_algo(piccl_comm* c, Coll coll, size_t bytes, int* k);
 Algo select_algo_n(int nranks, Coll coll, size_t bytes, int* k);
+// persistent launcher (PICCL_LAUNCH=persistent): PICCL_OK if enqueued through the server, PICCL_UNSUPPORTED: launch directly
+int persist_allreduce(piccl_comm** cs, int n, const LLArgs& la, const void* const* in, void* const* out, long long count, int dtype, int op, int avg,
+                      int algo, int k, cudaStream_t stream);
+void persist_destroy(piccl_comm* c);
 }  // namespace piccl

@@ -41,6 +41,8 @@ static void load() {
   e.tp_feeders = env_int("PICCL_TP_FEEDERS", 24); // CTAs that push the local shard in all-gather -> GEMM
   e.log_level = env_int("PICCL_LOG", 0);
   e.debug = env_int("PICCL_DEBUG", 0);
+  { const char* l = getenv("PICCL_LAUNCH"); e.launch_persistent = l && !strcmp(l, "persistent"); }
+  e.persist_idle_us = env_int("PICCL_PERSIST_IDLE_US", 500);
   const char* t = getenv("PICCL_TRACE"); e.trace_file = t ? t : "";
   const char* tf = getenv("PICCL_TUNE_FILE"); e.tune_file = tf ? tf : "";
   e.fault_rank = -1; e.fault_call = -1; e.fault_delay_ms = 0; e.fault_skip = false;

@@ -28,6 +28,7 @@ namespace piccl {
 using namespace sm100;
 typedef __nv_bfloat16 bf16;
 constexpr int TP_BN = 256, TP_STAGES = 4, TP_MAX_RANKS = 8;
+constexpr int RS_STAGES = 3, RS_STAGING = GEMM_BM * TP_BN * 2;   // reduce-scatter: one ring stage gives way to a 64 KiB staging tile
 
 __device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
   unsigned v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v;
@@ -69,7 +70,12 @@ struct TpArgs {
 // ------------------------------------------------------------------ GEMM -> reduce-scatter
 struct RsPolicy {
   const TpRank* R; int n, rank, N, mb_per_owner, num_n, tiles_per_owner, parity; unsigned epoch;
-  long long flag_off, data_off; int* s_ok;
+  long long flag_off, data_off; int* s_ok; uint8_t* staging;
+  static constexpr int STAGING = RS_STAGING;
+  __device__ void set_staging(uint8_t* p) { staging = p; }
+  // A tile travels as 128 rows of 512 bytes; inside every 128-byte group the 16-byte pieces are XOR-ed with the
+  // row number, which makes the epilogue's shared-memory stores conflict free.  Writer and reader use the same map.
+  __device__ static int piece_off(int row, int piece) { return row * (TP_BN * 2) + (((piece & ~7) | ((piece & 7) ^ (row & 7))) << 4); }
   __device__ int num_tiles() const { return n * tiles_per_owner; }
   __device__ void tile(int idx, int& m_blk, int& n_blk) const {
     const int owner = (rank + 1 + idx / tiles_per_owner) % n, within = idx % tiles_per_owner;
@@ -95,7 +101,18 @@ struct RsPolicy {
   }
   __device__ void store(int m_blk, int n_blk, int row, int col0, float (&v)[32]) {
     const int owner = m_blk / mb_per_owner, t = tile_id(m_blk, n_blk);
-    if (owner != rank) { store_row32_bf16(inbox(owner, rank, t) + (size_t)row * TP_BN + col0, v); return; }
+    if (owner != rank) {
+      // remote tile: into the staging tile; tile_end ships it with one bulk store
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        uint4 o; __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int q = 0; q < 4; q++) o2[q] = __floats2bfloat162_rn(v[8 * j + 2 * q], v[8 * j + 2 * q + 1]);
+        *reinterpret_cast<uint4*>(staging + piece_off(row, col0 / 8 + j)) = o;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // these stores must be visible to the bulk-copy engine
+      return;
+    }
     float sum[32];
 #pragma unroll
     for (int i = 0; i < 32; i++) sum[i] = 0.f;
@@ -103,13 +120,33 @@ struct RsPolicy {
       if (src == rank) {
 #pragma unroll
         for (int i = 0; i < 32; i++) sum[i] += v[i];
-      } else add_row32_bf16_volatile(inbox(rank, src, t) + (size_t)row * TP_BN + col0, sum);
+      } else {
+        const char* tile = reinterpret_cast<const char*>(inbox(rank, src, t));
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          uint4 b;
+          asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(tile + piece_off(row, col0 / 8 + j)) : "memory");
+          const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+          for (int q = 0; q < 4; q++) { float2 f = __bfloat1622float2(b2[q]); sum[8 * j + 2 * q] += f.x; sum[8 * j + 2 * q + 1] += f.y; }
+        }
+      }
     }
     store_row32_bf16(R->out + (size_t)((m_blk % mb_per_owner) * GEMM_BM + row) * N + (size_t)n_blk * TP_BN + col0, sum);
   }
   __device__ void tile_end(int m_blk, int n_blk, int et) {
     const int owner = m_blk / mb_per_owner;
-    if (owner != rank && et == 0) st_release_sys_u32(flag_ptr(owner, rank, tile_id(m_blk, n_blk)), epoch);
+    if (owner == rank) return;
+    // all 128 threads have written the staging tile (barrier passed): one asynchronous bulk store moves the 64 KiB over NVLink
+    if (et == 0) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      bulk_store(inbox(owner, rank, tile_id(m_blk, n_blk)), staging, RS_STAGING);
+      bulk_commit();
+      bulk_wait_all();                              // data written; then tell the owner
+      asm volatile("fence.proxy.async;" ::: "memory");
+      st_release_sys_u32(flag_ptr(owner, rank, tile_id(m_blk, n_blk)), epoch);
+    }
+    epilogue_barrier();                             // the staging tile is free again
   }
 };
 
@@ -119,8 +156,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_rs_kernel(const __grid_c
   const int vr = blockIdx.x / a.ctas_per_rank, cta = blockIdx.x % a.ctas_per_rank;
   const TpRank* R = &a.r[vr];
   if (threadIdx.x == 0) { s_abort = 0; s_ok = 1; tma_prefetch_desc(&R->ta); }
-  RsPolicy pol{R, a.n, R->rank, a.N, a.M / a.n / GEMM_BM, a.N / TP_BN, (a.M / a.n / GEMM_BM) * (a.N / TP_BN), (int)(a.epoch & 1), a.epoch, a.flag_off, a.data_off, &s_ok};
-  gemm_persistent<TP_BN, TP_STAGES>(smem_raw, &R->tb, pol, a.K, cta, a.ctas_per_rank, R->status, &s_abort);
+  RsPolicy pol{R, a.n, R->rank, a.N, a.M / a.n / GEMM_BM, a.N / TP_BN, (a.M / a.n / GEMM_BM) * (a.N / TP_BN), (int)(a.epoch & 1), a.epoch, a.flag_off, a.data_off, &s_ok, nullptr};
+  gemm_persistent<TP_BN, RS_STAGES>(smem_raw, &R->tb, pol, a.K, cta, a.ctas_per_rank, R->status, &s_abort);
 }
 
 // ------------------------------------------------------------------ all-gather -> GEMM
@@ -143,6 +180,8 @@ struct AgPolicy {
     asm volatile("fence.proxy.async;" ::: "memory");   // the rows were written with ordinary stores; TMA reads them through the async proxy
     return true;
   }
+  static constexpr int STAGING = 0;
+  __device__ void set_staging(uint8_t*) {}
   __device__ bool tile_begin(int, int, int, volatile int*) { return true; }
   __device__ void tile_end(int, int, int) {}
   __device__ void store(int m_blk, int n_blk, int row, int col0, float (&v)[32]) {
@@ -233,15 +272,15 @@ static int tp_launch(piccl_comm** cs, int n, const void* const* A, const void* c
     ok &= make_tmap_bf16_k64(&R.tb, B[i], (uint64_t)N, (uint64_t)K, (uint64_t)K, TP_BN);
   }
   if (!ok) { if (prev != c0->device && prev >= 0) cudaSetDevice(prev); return fail(PICCL_CUDA_ERROR, "tensor map or status set-up failed"); }
-  typedef GemmSmem<TP_BN, TP_STAGES> L;
+  const int smem_bytes = which ? GemmSmem<TP_BN, TP_STAGES>::DYNAMIC : GemmSmem<TP_BN, RS_STAGES, RS_STAGING>::DYNAMIC;
   const void* fn = which ? (const void*)ag_gemm_kernel : (const void*)gemm_rs_kernel;
   static bool attr[2] = {false, false};
-  if (!attr[which]) { if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYNAMIC) != cudaSuccess) return fail(PICCL_CUDA_ERROR, "cannot get %d bytes of shared memory", L::DYNAMIC); attr[which] = true; }
+  if (!attr[which]) { if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return fail(PICCL_CUDA_ERROR, "cannot get %d bytes of shared memory", smem_bytes); attr[which] = true; }
   void* args[] = {&a};
   cudaError_t e;
   // ranks wait for one another inside the kernel: several virtual ranks on one device must be co-resident
-  if (n > 1) e = cudaLaunchCooperativeKernel(fn, dim3(n * a.ctas_per_rank), dim3(GEMM_THREADS), args, L::DYNAMIC, stream);
-  else e = cudaLaunchKernel(fn, dim3(a.ctas_per_rank), dim3(GEMM_THREADS), args, L::DYNAMIC, stream);
+  if (n > 1) e = cudaLaunchCooperativeKernel(fn, dim3(n * a.ctas_per_rank), dim3(GEMM_THREADS), args, smem_bytes, stream);
+  else e = cudaLaunchKernel(fn, dim3(a.ctas_per_rank), dim3(GEMM_THREADS), args, smem_bytes, stream);
   if (prev != c0->device && prev >= 0) cudaSetDevice(prev);
   if (e != cudaSuccess) return fail(PICCL_CUDA_ERROR, "fused kernel launch failed: %s", cudaGetErrorString(e));
   for (int i = 0; i < n; i++) cs[i]->stats.launches++;

@@ -219,6 +219,17 @@ def test_low_latency_path_matches_fifo_path(groups):
                 assert torch.equal(outs[r], outs[0])
 
 
+def test_persistent_launcher_serves_and_leaves():
+    # separate process: the launch mode is read from the environment when the library is loaded
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    env = dict(os.environ, PICCL_LAUNCH="persistent", PICCL_PERSIST_IDLE_US="300")
+    r = subprocess.run([sys.executable, str(Path(__file__).parent / "persistent_worker.py")], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "PERSISTENT_OK 45" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
 def test_bounded_wait_reports_instead_of_hanging():
     # a wait for data nobody sends runs into its limit; the kernel returns, the status says where
     from piccl_b200.parallel.comm import LoopbackGroup, make_config
