@@ -22,6 +22,7 @@ namespace piccl {
 constexpr int kFlagStride = 128;          // bytes between two counters
 constexpr int kMaxVRanks = 8;             // virtual ranks one launch can carry (single-GPU emulation)
 constexpr int kMaxBlock = 512;
+constexpr int kLLFifoCta = 8, kLLFifoSlots = 8, kLLFifoSlotBytes = 8192;   // low-latency FIFO: CTAs, ring depth, bytes per slot (half of it payload)
 
 struct RankCtx {
   int rank, nranks, max_cta, nslot;
@@ -29,10 +30,13 @@ struct RankCtx {
   long long tail_off, head_off, ll_off, scratch_off, fifo_off, heap_bytes;
   long long ll_slot_bytes;                // bytes of one low-latency slot (2 x the largest payload)
   long long scratch_bytes;
+  long long llf_off, llf_head_off;                // low-latency FIFO of the executor: lines and head counters
   long long tp_flag_off, tp_data_off, tp_bytes;   // tensor-parallel workspace: epoch flags (1 MiB, zeroed) and payload
   char* heap[kMaxRanks];                  // every rank's heap as mapped in this process
   unsigned long long* sent;               // [nranks * max_cta] entries pushed per (peer, cta)
   unsigned long long* rcvd;               // [nranks * max_cta] entries consumed per (peer, cta)
+  unsigned long long* sent_ll;            // [nranks * kLLFifoCta] the same for the low-latency FIFO
+  unsigned long long* rcvd_ll;
   int* abort_flag;                        // device memory; non-zero: every wait gives up
   piccl_status_t* status;                 // pinned host memory, device address
 };
@@ -86,5 +90,7 @@ typedef void (*ExecKernelFn)(KernelArgs);
 // [dtype][op 0..3]; filled by the exec_inst_*.cu translation units.
 ExecKernelFn exec_kernel_for(int dtype, int op);
 ExecKernelFn exec_copy_kernel();
+ExecKernelFn exec_ll_kernel_for(int dtype, int op);   // low-latency variant (exec_ll.cuh)
+ExecKernelFn exec_ll_copy_kernel();
 
 }  // namespace piccl

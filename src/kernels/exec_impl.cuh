@@ -368,9 +368,5 @@ __global__ void __launch_bounds__(kMaxBlock, 1) exec_kernel(const KernelArgs ka)
   if (tid < nranks) { ctx->sent[tid * max_cta + cta] = my_sent; ctx->rcvd[tid * max_cta + cta] = my_rcvd; }
 }
 
-#define PICCL_INSTANTIATE_EXEC(T, DT)                                                              \
-  namespace piccl {                                                                                \
-  ExecKernelFn exec_table_##DT[4] = {exec_kernel<T, 0>, exec_kernel<T, 1>, exec_kernel<T, 2>, exec_kernel<T, 3>}; \
-  }
 
 }  // namespace piccl

@@ -1,3 +1,3 @@
 // Executor instantiations for one element type (sum, prod, max, min).
-#include "exec_impl.cuh"
+#include "exec_ll.cuh"
 PICCL_INSTANTIATE_EXEC(uint32_t, U32)

@@ -94,7 +94,11 @@ int piccl_comm_create(int rank, int nranks, int device, const piccl_config_t* us
   c->cfg.tp_bytes = cfg.tp_bytes;
   const long long tp_flags = cfg.tp_bytes > 0 ? (1 << 20) : 0;
   x.tail_off = 0; x.head_off = flags; x.ll_off = 2 * flags; x.tp_flag_off = x.ll_off + ll_bytes;
-  x.scratch_off = x.tp_flag_off + tp_flags; x.scratch_bytes = round_up(cfg.scratch_bytes, 4096);
+  // low-latency FIFO of the executor (all collectives, small messages): head counters, then the lines
+  x.llf_head_off = x.tp_flag_off + tp_flags;
+  x.llf_off = x.llf_head_off + round_up((long long)nranks * kLLFifoCta * kFlagStride, 4096);
+  x.scratch_off = x.llf_off + (long long)nranks * kLLFifoCta * kLLFifoSlots * kLLFifoSlotBytes; x.scratch_bytes = round_up(cfg.scratch_bytes, 4096);
+  c->llf_max_bytes = (long long)e.llf_kb * 1024;
   c->ll_max_bytes = ll_payload;
   x.fifo_off = x.scratch_off + x.scratch_bytes;
   x.tp_data_off = round_up(x.fifo_off + (long long)nranks * cfg.max_cta * cfg.nslot * cfg.slot_bytes, 4096);
@@ -109,6 +113,9 @@ int piccl_comm_create(int rank, int nranks, int device, const piccl_config_t* us
   size_t cnt_bytes = (size_t)nranks * cfg.max_cta * sizeof(unsigned long long);
   CREATE_TRY(cudaMalloc(&c->d_sent, cnt_bytes)); CREATE_TRY(cudaMemset(c->d_sent, 0, cnt_bytes));
   CREATE_TRY(cudaMalloc(&c->d_rcvd, cnt_bytes)); CREATE_TRY(cudaMemset(c->d_rcvd, 0, cnt_bytes));
+  size_t cnt_ll = (size_t)nranks * kLLFifoCta * sizeof(unsigned long long);
+  CREATE_TRY(cudaMalloc(&c->d_sent_ll, cnt_ll)); CREATE_TRY(cudaMemset(c->d_sent_ll, 0, cnt_ll));
+  CREATE_TRY(cudaMalloc(&c->d_rcvd_ll, cnt_ll)); CREATE_TRY(cudaMemset(c->d_rcvd_ll, 0, cnt_ll));
   CREATE_TRY(cudaMalloc(&c->d_abort, sizeof(int))); CREATE_TRY(cudaMemset(c->d_abort, 0, sizeof(int)));
   CREATE_TRY(cudaHostAlloc(&c->h_status, sizeof(piccl_status_t), cudaHostAllocMapped));
   memset(c->h_status, 0, sizeof(piccl_status_t));
@@ -116,7 +123,7 @@ int piccl_comm_create(int rank, int nranks, int device, const piccl_config_t* us
   CREATE_TRY(cudaMalloc(&c->d_ctx, sizeof(RankCtx)));
   CREATE_TRY(cudaDeviceSynchronize());
 #undef CREATE_TRY
-  x.sent = c->d_sent; x.rcvd = c->d_rcvd; x.abort_flag = c->d_abort; x.status = c->d_status;
+  x.sent = c->d_sent; x.rcvd = c->d_rcvd; x.sent_ll = c->d_sent_ll; x.rcvd_ll = c->d_rcvd_ll; x.abort_flag = c->d_abort; x.status = c->d_status;
   int sms = 0; cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device); c->sm_count = sms > 0 ? sms : 148;
   log_msg(2, "comm %p: rank %d/%d dev %d heap %.1f MiB (max_cta %d nslot %d slot %lld KiB scratch %lld MiB)", (void*)c, rank, nranks, device,
           c->heap_bytes / 1048576.0, cfg.max_cta, cfg.nslot, cfg.slot_bytes >> 10, x.scratch_bytes >> 20);
@@ -189,6 +196,7 @@ int piccl_comm_destroy(piccl_comm_t* c) {
   for (auto& kv : c->cache) if (kv.second.ready) cudaEventDestroy(kv.second.ready);
   for (auto& t : c->trace) { if (t.start) cudaEventDestroy(t.start); if (t.stop) cudaEventDestroy(t.stop); }
   if (c->d_tp_status) cudaFree(c->d_tp_status);
+  cudaFree(c->d_sent_ll); cudaFree(c->d_rcvd_ll);
   cudaFree(c->heap); cudaFree(c->d_sent); cudaFree(c->d_rcvd); cudaFree(c->d_abort); cudaFree(c->d_ctx);
   if (c->h_status) cudaFreeHost(c->h_status);
   cudaGetLastError();
@@ -347,7 +355,9 @@ static int run(piccl_comm** comms, int n, const CallDesc* calls, cudaStream_t st
   // data-moving collectives run the byte-wise instantiation
   const int esz = reducing ? esz_real : 1;
   const long long count = reducing ? (long long)d0.count : (long long)d0.count * esz_real;
-  ExecKernelFn fn = reducing ? exec_kernel_for(d0.dtype, op) : exec_copy_kernel();
+  // small messages of every collective run the low-latency variant of the executor (flags inside the data lines)
+  const bool use_llf = c0->llf_max_bytes > 0 && (long long)d0.count * esz_real <= c0->llf_max_bytes;
+  ExecKernelFn fn = use_llf ? (reducing ? exec_ll_kernel_for(d0.dtype, op) : exec_ll_copy_kernel()) : (reducing ? exec_kernel_for(d0.dtype, op) : exec_copy_kernel());
   if (!fn) return fail(PICCL_INTERNAL_ERROR, "no kernel for dtype %d op %d", d0.dtype, op);
 
   // small exchange-type all-reduces take the low-latency kernel (flags travel inside the data lines)
@@ -432,7 +442,16 @@ static int run(piccl_comm** comms, int n, const CallDesc* calls, cudaStream_t st
       if (d.coll == COLL_REDUCE && c->rank != d.root) a.in_place = false;
       const ProgEntry* pe = nullptr;
       rc = get_program(c, a, stream, &pe); if (rc) break;
-      if (i == 0) { n_cta = choose_cta(c, a, n); ka.n_cta = n_cta; ka.timeout_ns = (unsigned long long)c->cfg.timeout_ms * 1000000ull; }
+      if (i == 0) {
+        n_cta = choose_cta(c, a, n);
+        if (use_llf) {   // 4 KiB of payload per CTA and segment, at most kLLFifoCta CTAs
+          long long ab = a.count * a.elem_size;
+          if (a.coll == COLL_ALLREDUCE && (a.algo == ALGO_RING || a.algo == ALGO_K_RING)) ab /= std::max(1, a.nranks);
+          n_cta = (int)std::max<long long>(1, std::min<long long>((ab + 4095) / 4096, kLLFifoCta));
+          if (n > 1) n_cta = std::min(n_cta, std::max(1, c->sm_count / n));
+        }
+        ka.n_cta = n_cta; ka.timeout_ns = (unsigned long long)c->cfg.timeout_ms * 1000000ull;
+      }
       ka.r[i].ctx = c->d_ctx; ka.r[i].actions = pe->dev; ka.r[i].n_actions = pe->n_actions; ka.r[i].in = s; ka.r[i].out = r;
       c->stats.launches++;
     }
@@ -444,8 +463,9 @@ static int run(piccl_comm** comms, int n, const CallDesc* calls, cudaStream_t st
     TraceRec* tr = trace_begin(c0, d0.coll, d0.algo, d0.k, cur * esz, n_cta, stream);
     void* args[] = {&ka};
     cudaError_t e;
-    if (n > 1) e = cudaLaunchCooperativeKernel((const void*)fn, dim3(n * n_cta), dim3(c0->cfg.block_size), args, 0, stream);
-    else e = cudaLaunchKernel((const void*)fn, dim3(n_cta), dim3(c0->cfg.block_size), args, 0, stream);
+    const int block = use_llf ? kLLBlock : c0->cfg.block_size;
+    if (n > 1) e = cudaLaunchCooperativeKernel((const void*)fn, dim3(n * n_cta), dim3(block), args, 0, stream);
+    else e = cudaLaunchKernel((const void*)fn, dim3(n_cta), dim3(block), args, 0, stream);
     if (e != cudaSuccess) rc = fail(PICCL_CUDA_ERROR, "executor launch failed: %s", cudaGetErrorString(e));
     trace_end(c0, tr, stream);
   }

@@ -49,7 +49,8 @@ struct piccl_comm {
   unsigned long long host_id = 0;
   char* heap = nullptr; long long heap_bytes = 0;
   piccl::RankCtx h_ctx{}; piccl::RankCtx* d_ctx = nullptr;
-  unsigned long long *d_sent = nullptr, *d_rcvd = nullptr; int* d_abort = nullptr;
+  unsigned long long *d_sent = nullptr, *d_rcvd = nullptr, *d_sent_ll = nullptr, *d_rcvd_ll = nullptr; int* d_abort = nullptr;
+  long long llf_max_bytes = 0;         // largest message the low-latency executor takes (0: off)
   piccl_status_t* h_status = nullptr; piccl_status_t* d_status = nullptr;
   bool ipc_opened[piccl::kMaxRanks] = {false};
   bool connected = false, broken = false;
