@@ -1,7 +1,9 @@
 #!/bin/bash
 # Collective sweeps for the baseline table: this library, stock NCCL and the reference build, same harness
 # (coll_bench), only LD_PRELOAD and the PICCL_* variables change.
-#   benchmarks/run_sweeps.sh N OUTDIR [quick]
+#   benchmarks/run_sweeps.sh N OUTDIR [quick|lean]
+# quick: fewer iterations and smaller maxima; lean: additionally every second size and a reduced set of variants
+# (what fits a few minutes on 8 GPUs).
 # Writes OUTDIR/sweep_<N>.csv (all rows) .  Reference rows are only produced for configurations in which the
 # reference is valid (fp32/int32, allreduce all algorithms, allgather RING/K_RING/PRD/PRM with k a power that
 # fits, reduce RING, broadcast RING/K_RING in place); its stubs and unsafe configurations are not run.
@@ -10,14 +12,38 @@ HERE="$(cd "$(dirname "$0")/.." && pwd)"; cd "$HERE"
 CB=piccl_b200/lib/coll_bench; OURS=piccl_b200/lib/piccl.so; REF=baseline/_ref/piccl.so
 mkdir -p "$OUT"; CSV="$OUT/sweep_$N.csv"; : > "$CSV"
 IS=1000; IL=100; [ -n "$QUICK" ] && { IS=200; IL=20; }
+STEP=2; AR_MIN=8; LEAN=""; [ "$QUICK" = "lean" ] && { STEP=4; AR_MIN=16; LEAN=1; }
 run() {  # label preload coll algo k dtype min max extra...
   local label=$1 pre=$2 coll=$3 algo=$4 k=$5 dt=$6 min=$7 max=$8; shift 8
   local up; up=$(echo "$coll" | tr a-z A-Z)
   env ${pre:+LD_PRELOAD=$pre} ${algo:+PICCL_${up}_ALGO=$algo} ${k:+PICCL_${up}_K=$k} timeout 300 $CB --gpus $N --coll $coll --dtype $dt --min $min --max $max \
-      --check --label "$label" --iters-small $IS --iters-large $IL "$@" 2>/dev/null | grep -v "^#\|^\[PICCL\|NCCL version\|PICCL_" >> "$CSV"
+      --check --label "$label" --iters-small $IS --iters-large $IL --step $STEP "$@" 2>/dev/null | grep -v "^#\|^\[PICCL\|NCCL version\|PICCL_" >> "$CSV"
 }
 KS="2 4"; [ "$N" -ge 8 ] && KS="2 4 8"
-AR_MAX=1073741824; BLK_MAX=268435456; [ -n "$QUICK" ] && { AR_MAX=268435456; BLK_MAX=67108864; }
+AR_MAX=1073741824; BLK_MAX=268435456; [ "$QUICK" = "quick" ] && { AR_MAX=268435456; BLK_MAX=67108864; }
+if [ -n "$LEAN" ]; then
+  # ---- reduced set
+  run nccl "" allreduce "" "" float $AR_MIN $AR_MAX
+  for spec in "RING -" "PRD -" "PRM 2" "PRM $N" "K_RING 4"; do set -- $spec; k=$2; [ "$k" = "-" ] && k=""; run ours-$1-k${k:--1} $OURS allreduce $1 "$k" float $AR_MIN $AR_MAX; done
+  if [ -f $REF ]; then run ref-RING $REF allreduce RING "" float $AR_MIN $AR_MAX; run ref-PRD $REF allreduce PRD "" float $AR_MIN $AR_MAX; run ref-PRM-k$N $REF allreduce PRM $N float $AR_MIN $AR_MAX; fi
+  run nccl "" allreduce "" "" bf16 $AR_MIN $AR_MAX
+  for spec in "RING -" "PRD -" "PRM $N"; do set -- $spec; k=$2; [ "$k" = "-" ] && k=""; run ours-$1-k${k:--1} $OURS allreduce $1 "$k" bf16 $AR_MIN $AR_MAX; done
+  for coll in allgather reduce_scatter reduce broadcast; do
+    run nccl "" $coll "" "" float 1024 $BLK_MAX
+    run ours-RING-k-1 $OURS $coll RING "" float 1024 $BLK_MAX
+    run ours-PRD-k-1 $OURS $coll PRD "" float 1024 $BLK_MAX
+    run ours-PRM-k2 $OURS $coll PRM 2 float 1024 $BLK_MAX
+    run nccl "" $coll "" "" bf16 1024 $BLK_MAX
+    run ours-RING-k-1 $OURS $coll RING "" bf16 1024 $BLK_MAX
+  done
+  if [ -f $REF ]; then
+    run ref-RING $REF allgather RING "" float 1024 $BLK_MAX
+    run ref-PRD $REF allgather PRD "" float 1024 $BLK_MAX
+    run ref-RING $REF reduce RING "" float 1024 $BLK_MAX
+    run ref-RING $REF broadcast RING "" float 1024 $BLK_MAX --in-place
+  fi
+  echo "rows: $(wc -l < "$CSV")"; exit 0
+fi
 # ---- allreduce, fp32 and bf16
 for dt in float bf16; do
   run nccl "" allreduce "" "" $dt 8 $AR_MAX

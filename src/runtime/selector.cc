@@ -38,16 +38,19 @@ Algo select_algo_n(int n, Coll coll, size_t bytes, int* k) {
   std::call_once(g_once, load_table);
   for (auto& r : g_rows)
     if (r.coll == coll && r.nranks == n && (long long)bytes <= r.max_bytes) { if (k) *k = r.k; return r.algo; }
+  // Built-in rule (measured on B200 NVLink): one exchange with every rank while the message is tiny, recursive
+  // doubling on the low-latency path up to 1 MiB, the bandwidth-optimal ring above.
   int kk = n < 8 ? n : 8;
   switch (coll) {
     case COLL_ALLREDUCE:
-      if (bytes <= (size_t)256 << 10) { if (k) *k = kk; return ALGO_PRM; }
+      if (bytes <= (size_t)32 << 10) { if (k) *k = kk; return ALGO_PRM; }
+      if (bytes <= (size_t)1 << 20) { if (k) *k = 2; return ALGO_PRD; }
       return ALGO_RING;
     case COLL_ALLGATHER: case COLL_REDUCE_SCATTER:
-      if (bytes <= (size_t)1 << 20) { if (k) *k = kk; return ALGO_PRM; }
+      if (bytes <= (size_t)64 << 10) { if (k) *k = kk; return ALGO_PRM; }
       return ALGO_RING;
     default:
-      if (bytes <= (size_t)1 << 20) { if (k) *k = kk; return ALGO_PRM; }
+      if (bytes <= (size_t)64 << 10) { if (k) *k = 2; return ALGO_PRD; }
       return ALGO_RING;
   }
 }
