@@ -77,9 +77,17 @@ struct RsPolicy {
   // row number, which makes the epilogue's shared-memory stores conflict free.  Writer and reader use the same map.
   __device__ static int piece_off(int row, int piece) { return row * (TP_BN * 2) + (((piece & ~7) | ((piece & 7) ^ (row & 7))) << 4); }
   __device__ int num_tiles() const { return n * tiles_per_owner; }
+  // Order: panels of 16 column blocks (one panel of B stays in L2); inside a panel the owners (rank+1, rank+2, ..., myself
+  // last); inside an owner's block rows fastest.  All ranks walk the panels in the same order, so the partials of my own
+  // tiles of a panel are on their way while I still compute the other owners' tiles of that panel.
   __device__ void tile(int idx, int& m_blk, int& n_blk) const {
-    const int owner = (rank + 1 + idx / tiles_per_owner) % n, within = idx % tiles_per_owner;
-    m_blk = owner * mb_per_owner + within % mb_per_owner; n_blk = within / mb_per_owner;
+    constexpr int PN = 16;
+    const int per_panel = PN * mb_per_owner * n;              // tiles of a full panel
+    const int panel = idx / per_panel; int within = idx % per_panel;
+    const int cols = min(PN, num_n - panel * PN);             // last panel may be narrower
+    const int per_owner = cols * mb_per_owner;
+    const int owner = (rank + 1 + within / per_owner) % n; within %= per_owner;
+    m_blk = owner * mb_per_owner + within % mb_per_owner; n_blk = panel * PN + within / mb_per_owner;
   }
   __device__ const CUtensorMap* a_map(int m_blk, int& row0) const { row0 = m_blk * GEMM_BM; return &R->ta; }
   __device__ bool gate(int, volatile int*) const { return true; }
