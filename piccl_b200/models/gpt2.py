@@ -94,6 +94,7 @@ class GPT2:
         self.m = torch.zeros_like(self.master)
         self.v = torch.zeros_like(self.master)
         self.step_count = 0
+        self.step_dev = torch.zeros(1, dtype=torch.int32, device=self.device)     # the same counter on the device (graph replay)
         self._bufs: dict = {}
         self._wte_stage: Optional[torch.Tensor] = None
 
@@ -223,10 +224,12 @@ class GPT2:
 
     # ------------------------------------------------------------------ optimizer
     def optimizer_step(self, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.1) -> None:
+        """Fused AdamW over the flat buffers; the step number lives on the device so that the launches can be replayed."""
         self.step_count += 1
+        self.step_dev.add_(1)
         for b, e, decay in self.groups:
-            ops.adamw(self.flat_p[b:e], self.master[b:e], self.m[b:e], self.v[b:e], self.flat_g[b:e], lr, betas[0], betas[1], eps,
-                      weight_decay if decay else 0.0, self.step_count)
+            ops.adamw_devstep(self.flat_p[b:e], self.master[b:e], self.m[b:e], self.v[b:e], self.flat_g[b:e], lr, betas[0], betas[1], eps,
+                              weight_decay if decay else 0.0, self.step_dev)
 
     @torch.no_grad()
     def loss(self, idx: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:

@@ -101,6 +101,13 @@ def adamw(p, master, m, v, g, lr: float, b1: float, b2: float, eps: float, wd: f
     _bump()
 
 
+def adamw_devstep(p, master, m, v, g, lr: float, b1: float, b2: float, eps: float, wd: float, step_dev, gscale: float = 1.0):
+    """AdamW with the step number in a device int32 tensor (replayable from a CUDA graph)."""
+    _chk(N.ops_lib().piccl_ops_adamw_devstep(_p(p), _p(master), _p(m), _p(v), _p(g), C.c_longlong(p.numel()), C.c_float(lr), C.c_float(b1), C.c_float(b2),
+                                             C.c_float(eps), C.c_float(wd), _p(step_dev), C.c_float(gscale), C.c_void_p(_s())), "adamw_devstep")
+    _bump()
+
+
 def embed_fwd(idx, wte, wpe, out, seq: int):
     rows, Cc = out.shape
     _chk(N.ops_lib().piccl_ops_embed_fwd(_p(idx), _p(wte), _p(wpe), _p(out), rows, seq, Cc, C.c_void_p(_s())), "embed_fwd")

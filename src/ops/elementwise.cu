@@ -122,7 +122,11 @@ __global__ void __launch_bounds__(512) ce_fwd_bwd_kernel(bf16* __restrict__ logi
 // AdamW on flat buffers: bf16 gradient and parameter, fp32 master copy and moments.
 __global__ void __launch_bounds__(256) adamw_kernel(bf16* __restrict__ p, float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
                                                     const bf16* __restrict__ g, size_t n8, float lr, float b1, float b2, float eps, float wd,
-                                                    float bc1, float bc2, float gscale) {
+                                                    float bc1, float bc2, float gscale, const int* __restrict__ step_dev) {
+  if (step_dev) {   // step number kept on the device (the launch can then be replayed from a CUDA graph)
+    const float st = (float)*step_dev;
+    bc1 = 1.f - powf(b1, st); bc2 = 1.f - powf(b2, st);
+  }
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
     float gv[8]; unpack8(reinterpret_cast<const bf16x8*>(g)[i], gv);
     float4 w0 = reinterpret_cast<float4*>(master)[2 * i], w1 = reinterpret_cast<float4*>(master)[2 * i + 1];
@@ -229,7 +233,14 @@ int piccl_ops_adamw(void* p, float* master, float* m, float* v, const void* g, l
                     int step, float gscale, void* stream) {
   if (n % 8) return -1;
   float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
-  adamw_kernel<<<grid_for(n / 8, 256), 256, 0, (cudaStream_t)stream>>>((bf16*)p, master, m, v, (const bf16*)g, (size_t)n / 8, lr, b1, b2, eps, wd, bc1, bc2, gscale);
+  adamw_kernel<<<grid_for(n / 8, 256), 256, 0, (cudaStream_t)stream>>>((bf16*)p, master, m, v, (const bf16*)g, (size_t)n / 8, lr, b1, b2, eps, wd, bc1, bc2, gscale, nullptr);
+  PICCL_OPS_CHECK_LAUNCH(); return 0;
+}
+// Same update with the step number read from device memory (`step_dev`, an int the caller advances on the device).
+int piccl_ops_adamw_devstep(void* p, float* master, float* m, float* v, const void* g, long long n, float lr, float b1, float b2, float eps, float wd,
+                            const int* step_dev, float gscale, void* stream) {
+  if (n % 8 || !step_dev) return -1;
+  adamw_kernel<<<grid_for(n / 8, 256), 256, 0, (cudaStream_t)stream>>>((bf16*)p, master, m, v, (const bf16*)g, (size_t)n / 8, lr, b1, b2, eps, wd, 1.f, 1.f, gscale, step_dev);
   PICCL_OPS_CHECK_LAUNCH(); return 0;
 }
 int piccl_ops_embed_fwd(const long long* idx, const void* wte, const void* wpe, void* out, int rows, int S, int C, void* stream) {

@@ -361,7 +361,10 @@ static int run(piccl_comm** comms, int n, const CallDesc* calls, cudaStream_t st
   if (!fn) return fail(PICCL_INTERNAL_ERROR, "no kernel for dtype %d op %d", d0.dtype, op);
 
   // small exchange-type all-reduces take the low-latency kernel (flags travel inside the data lines)
-  if (d0.coll == COLL_ALLREDUCE && c0->ll_max_bytes > 0 && (long long)d0.count * esz_real <= c0->ll_max_bytes &&
+  // (not while the stream is being captured: the call epoch is a launch argument, a replay would reuse it)
+  cudaStreamCaptureStatus cap_state = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap_state) != cudaSuccess) { cudaGetLastError(); cap_state = cudaStreamCaptureStatusNone; }
+  if (cap_state == cudaStreamCaptureStatusNone && d0.coll == COLL_ALLREDUCE && c0->ll_max_bytes > 0 && (long long)d0.count * esz_real <= c0->ll_max_bytes &&
       (d0.algo == ALGO_RD || d0.algo == ALGO_RM || d0.algo == ALGO_PRD || d0.algo == ALGO_PRM)) {
     Resolved rs = resolve(COLL_ALLREDUCE, d0.algo, d0.k, c0->nranks);
     LLKernelFn lf = ll_kernel_for(d0.dtype, op);
