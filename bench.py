@@ -242,11 +242,20 @@ def reexec_under_reference():
             torch_nccl = cand
     if torch_nccl is None:
         return "PyTorch's bundled libnccl.so.2 not found"
+    # all ranks of a node run this at the same time: make the links atomically and tolerate a rank that was faster
     for name in ("libnccl.so", "libnccl.so.2"):
         link = shim_dir / name
-        if link.is_symlink() or link.exists():
-            link.unlink()
-        link.symlink_to(torch_nccl)
+        try:
+            if link.is_symlink() and os.readlink(link) == str(torch_nccl):
+                continue
+            tmp = shim_dir / f".{name}.{os.getpid()}"
+            if tmp.is_symlink() or tmp.exists():
+                tmp.unlink()
+            tmp.symlink_to(torch_nccl)
+            os.replace(tmp, link)
+        except OSError:
+            if not link.exists():
+                return f"cannot create {link}"
     env = dict(os.environ)
     env["LD_PRELOAD"] = str(reference_paths())
     env["LD_LIBRARY_PATH"] = f"{shim_dir}:/usr/local/cuda/lib64:" + env.get("LD_LIBRARY_PATH", "")
