@@ -39,10 +39,14 @@ def main(paths):
         sizes = sorted(b for c, d, m, b in rows if (c, d, m) == (coll, dt, n))
         labels = sorted({l for (c, d, m, b), v in rows.items() if (c, d, m) == (coll, dt, n) for l in v},
                         key=lambda l: (0 if l == "nccl" else 1 if l.startswith("ref") else 2, l))
-        small = [b for b in sizes if b <= 65536][::2][:6]
-        large = [b for b in sizes if b >= (1 << 20)][::2]
+        small = [b for b in sizes if b <= 65536]
+        large = [b for b in sizes if b >= (1 << 20)]
+        if len(small) > 6:
+            small = small[::2][:6]
+        if len(large) > 7:
+            large = large[::2]
         print(f"\n#### {coll}, {dt}, {n} GPUs — latency µs (small) / busBW GB/s (large); † = failed the data check\n")
-        print("| impl | " + " | ".join(f"{b} B" for b in small) + " | " + " | ".join(f"{b >> 20} MiB" for b in large) + " |")
+        print("| impl | " + " | ".join(f"{b} B" for b in small) + " | " + " | ".join((f"{b >> 30} GiB" if b >= (1 << 30) else f"{b >> 20} MiB") for b in large) + " |")
         print("|---|" + "---|" * (len(small) + len(large)))
         for l in labels:
             cells = [fmt(rows[(coll, dt, n, b)].get(l), None, False) for b in small] + [fmt(rows[(coll, dt, n, b)].get(l), None, True) for b in large]
