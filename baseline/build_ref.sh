@@ -5,10 +5,10 @@
 #   * -I$CUDA_HOME/include/nvtx3   (CUDA >= 12.9 ships <nvToolsExt.h> only under nvtx3/)
 #   * no -lnvToolsExt              (NVTX3 is header only)
 #   * -gencode arch=compute_100,code=sm_100 (the reference passes no arch at all)
-# Usage: baseline/build_ref.sh [reference_root]   (default /root/reference)
+# Usage: baseline/build_ref.sh [reference_root]   (default: $PICCL_REFERENCE_ROOT, else the reference checkout mounted beside this repository)
 set -e
 HERE="$(cd "$(dirname "$0")" && pwd)"
-REF="${1:-/root/reference}"
+REF="${1:-${PICCL_REFERENCE_ROOT:-$HERE/../../reference}}"
 CUDA_HOME="${CUDA_HOME:-/usr/local/cuda}"
 OUT="$HERE/_ref"
 if [ ! -d "$REF/src" ] && [ -d "$OUT/src" ]; then REF="$OUT"; fi

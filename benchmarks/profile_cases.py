@@ -8,7 +8,7 @@
     python benchmarks/profile_cases.py ce        # cross entropy forward+backward, 8192 x 50304
 
 Typical capture (after the same command has exited 0 without ncu):
-    ncu --set full --clock-control none -k regex:<kernel> -s 2 -c 2 -o gpurun_out/<name> python benchmarks/profile_cases.py <case>
+    ncu --set full --clock-control none -k regex:<kernel> -s 2 -c 2 -o <name> python benchmarks/profile_cases.py <case>
 """
 from __future__ import annotations
 

@@ -7,7 +7,7 @@
 # Writes OUTDIR/sweep_<N>.csv (all rows) .  Reference rows are only produced for configurations in which the
 # reference is valid (fp32/int32, allreduce all algorithms, allgather RING/K_RING/PRD/PRM with k a power that
 # fits, reduce RING, broadcast RING/K_RING in place); its stubs and unsafe configurations are not run.
-N=${1:-2}; OUT=${2:-gpurun_out}; QUICK=${3:-}
+N=${1:-2}; OUT=${2:-results}; QUICK=${3:-}
 HERE="$(cd "$(dirname "$0")/.." && pwd)"; cd "$HERE"
 CB=piccl_b200/lib/coll_bench; OURS=piccl_b200/lib/piccl.so; REF=baseline/_ref/piccl.so
 mkdir -p "$OUT"; CSV="$OUT/sweep_$N.csv"; : > "$CSV"

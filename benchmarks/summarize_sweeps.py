@@ -1,8 +1,8 @@
-"""Turns coll_bench sweep CSVs (benchmarks/run_sweeps.sh) into the markdown tables of BASELINE.md:
+"""Turns coll_bench sweep CSVs (benchmarks/run_sweeps.sh) into markdown tables:
 per collective / dtype / rank count, latency at small sizes and bus bandwidth at large sizes for
 stock NCCL, the reference build and every algorithm of this library.
 
-    python benchmarks/summarize_sweeps.py gpurun_out/sweep_8.csv [more.csv ...]
+    python benchmarks/summarize_sweeps.py results/sweep_8.csv [more.csv ...]
 """
 from __future__ import annotations
 

@@ -108,7 +108,7 @@ bool bootstrap(ShimComm* s, ncclComm_t comm) {
     cudaMemcpyAsync(all, dbuf, (size_t)n * sizeof mine, cudaMemcpyDeviceToHost, st);
     if (cudaStreamSynchronize(st) != cudaSuccess) { if (pc) piccl_comm_destroy(pc); break; }
     char good = created && piccl_comm_connect(pc, all) == PICCL_OK ? 1 : 0;
-    // round 2: one byte per rank
+    // second exchange: one byte per rank
     cudaMemcpyAsync(dbuf + r, &good, 1, cudaMemcpyHostToDevice, st);
     if (real_ag(dbuf + r, dbuf, 1, ncclChar, comm, st) != ncclSuccess) { if (pc) piccl_comm_destroy(pc); break; }
     char flags[kMaxRanks];

@@ -38,19 +38,24 @@ Algo select_algo_n(int n, Coll coll, size_t bytes, int* k) {
   std::call_once(g_once, load_table);
   for (auto& r : g_rows)
     if (r.coll == coll && r.nranks == n && (long long)bytes <= r.max_bytes) { if (k) *k = r.k; return r.algo; }
-  // Built-in rule (measured on B200 NVLink): one exchange with every rank while the message is tiny, recursive
-  // doubling on the low-latency path up to 1 MiB, the bandwidth-optimal ring above.
+  // Built-in rule, from sweeps on 2, 4 and 8 B200 (fp32 and bf16 sum):
+  //   all-reduce      <= 4 KiB one exchange with every rank (PRM, k = n: 8 us on 8 GPUs); up to 32 MiB (8 MiB on two
+  //                   ranks) recursive doubling, whose few steps beat the ring's 2(n-1) (222 vs 154 GB/s at 16 MiB on 8
+  //                   GPUs); above that the bandwidth-optimal ring (600 vs 290 GB/s at 256 MiB)
+  //   all-gather / reduce-scatter   one exchange with every rank while tiny, the ring otherwise (the ring was ahead of
+  //                   the recursive schedules from 1 KiB per rank upwards)
+  //   broadcast / reduce   the segment-pipelined chain at every size (8.5 us at 1 KiB, 581 GB/s at 256 MiB on 8 GPUs,
+  //                   the trees 8.8 us and 225 GB/s)
   int kk = n < 8 ? n : 8;
   switch (coll) {
     case COLL_ALLREDUCE:
-      if (bytes <= (size_t)32 << 10) { if (k) *k = kk; return ALGO_PRM; }
-      if (bytes <= (size_t)1 << 20) { if (k) *k = 2; return ALGO_PRD; }
+      if (bytes <= (size_t)4 << 10) { if (k) *k = kk; return ALGO_PRM; }
+      if (bytes <= ((size_t)(n <= 2 ? 8 : 32) << 20)) { if (k) *k = 2; return ALGO_PRD; }
       return ALGO_RING;
     case COLL_ALLGATHER: case COLL_REDUCE_SCATTER:
-      if (bytes <= (size_t)64 << 10) { if (k) *k = kk; return ALGO_PRM; }
+      if (bytes <= (size_t)16 << 10) { if (k) *k = kk; return ALGO_PRM; }
       return ALGO_RING;
     default:
-      if (bytes <= (size_t)64 << 10) { if (k) *k = 2; return ALGO_PRD; }
       return ALGO_RING;
   }
 }
