@@ -152,3 +152,66 @@ def test_selector_tables(tmp_path):
     assert select.main(["--from-bench", str(bench), "--output", str(out)]) == 0
     rows = [l.split(",") for l in out.read_text().splitlines() if not l.startswith("#")]
     assert rows[0][:5] == ["allreduce", "8", "8", "PRM", "8"] and rows[1][3] == "RING"
+
+
+# ---------------------------------------------------------------- per-rank lists and the matcher
+def _transfers(xml: str):
+    import re
+    return re.findall(r'<transfer id="(\d+)" size="(\d+)" src="(\d+)" dst="(\d+)" deps="([^"]*)"', xml)
+
+
+@pytest.mark.parametrize("coll", ["allgather", "allreduce", "bcast", "reduce", "reduce_scatter"])
+def test_matched_per_rank_lists_equal_the_native_dump(coll):
+    """Reference idea: tools/schedule_generator/saved/schedule_gen.py (a matcher of per-rank send / receive lists)."""
+    from tools.schedule_generator import per_rank as P
+    for algo, k in [("ring", 1), ("k_ring", 2), ("rd", 1), ("rm", 3), ("prd", 1), ("prm", 2), ("prm", 8)]:
+        for n in (2, 3, 4, 6, 8):
+            if algo == "k_ring" and n % k:
+                continue
+            size = 4096 * n
+            native = gen.generate(coll, n, size, algo, k)
+            matched = P.match(P.all_rank_lists(coll, n, size, algo, k), coll, algo, size)
+            assert _transfers(native) == _transfers(matched), (coll, algo, k, n)
+            ET.fromstring("\n".join(l for l in matched.splitlines() if not l.strip().startswith("#")))
+
+
+def test_per_rank_ring_allgather_lists_and_matcher_errors():
+    """Reference: saved/coll/allgather.py:16-62 — ring allgather as (sends, recvs) per rank."""
+    from tools.schedule_generator import per_rank as P
+    n, size = 4, 4096
+    for r in range(n):
+        sends, recvs = P.rank_lists("allgather", n, size, r)
+        assert [s["to"] for s in sends] == [(r + 1) % n] * (n - 1)
+        assert [rc["from"] for rc in recvs] == [(r - 1) % n] * (n - 1)
+        assert [s["tag"] for s in sends] == list(range(n - 1)) and all(s["size"] == size // n for s in sends)
+        # block (r-1-i) mod n lands at its own offset
+        assert [rc["offset"] for rc in recvs] == [((r - 1 - i) % n) * (size // n) for i in range(n - 1)]
+        # what is forwarded in step i is what arrived in step i-1
+        assert sends[0]["deps"] == [] and all(s["deps"] == [((r - 1) % n, i - 1)] for i, s in enumerate(sends) if i)
+    lists = P.all_rank_lists("allgather", n, size)
+    lists[2][1].pop()                      # rank 2 forgets its last receive
+    with pytest.raises(ValueError, match="no matching receive"):
+        P.match(lists, "allgather", "ring", size)
+    lists = P.all_rank_lists("allgather", n, size)
+    lists[1][0].pop()                      # rank 1 forgets its last send
+    with pytest.raises(ValueError, match="without a send"):
+        P.match(lists, "allgather", "ring", size)
+    lists = P.all_rank_lists("allgather", n, size)
+    lists[0][0][1]["size"] += 1
+    with pytest.raises(ValueError, match="meets receive"):
+        P.match(lists, "allgather", "ring", size)
+
+
+def test_standalone_k_ring_generator(tmp_path):
+    """Reference: saved/k-ring.py KRingScheduleGenerator (allgather / reduce / broadcast; allreduce was left empty)."""
+    from tools.schedule_generator import per_rank as P
+    for coll in ["allgather", "allreduce", "bcast", "reduce", "reduce_scatter"]:
+        xml = P.k_ring_xml(8, 8 * 4097, 2, coll)
+        assert 'algorithm="k_ring" k="2"' in xml and len(_transfers(xml)) > 0
+    with pytest.raises(ValueError, match="divisible"):
+        P.k_ring_xml(8, 4096, 3, "allgather")
+    out = subprocess.run([sys.executable, str(ROOT / "tools/schedule_generator/per_rank.py"), "--collective", "allgather", "--num_nodes", "4",
+                          "--buffer_size", "4096", "--rank", "1"], capture_output=True, text=True, check=True).stdout
+    import json
+    rec = json.loads(out.strip().splitlines()[-1])
+    assert rec["rank"] == 1 and len(rec["sends"]) == 3 and len(rec["recvs"]) == 3
