@@ -40,7 +40,7 @@ def parse():
     ap.add_argument("--preload", default="", help="with --impl ddp: library to LD_PRELOAD (e.g. piccl_b200/lib/piccl.so; PICCL_*_ALGO from the environment); empty: none")
     ap.add_argument("--model", default="medium", choices=["medium", "tiny"])
     ap.add_argument("--micro-batch", type=int, default=8)
-    ap.add_argument("--algo", default=None, help="all-reduce algorithm of the bucket reductions (RING, K_RING, RD, RM, PRD, PRM, AUTO)")
+    ap.add_argument("--algo", default=None, help="all-reduce algorithm of the bucket reductions (RING, K_RING, RD, RM, PRD, PRM, DIRECT, AUTO)")
     ap.add_argument("--k", type=int, default=-1)
     ap.add_argument("--no-collectives", action="store_true", help="skip the all-reduce sweep for N > 1")
     return ap.parse_args()

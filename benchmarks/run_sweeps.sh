@@ -24,15 +24,16 @@ AR_MAX=1073741824; BLK_MAX=268435456; [ "$QUICK" = "quick" ] && { AR_MAX=2684354
 if [ -n "$LEAN" ]; then
   # ---- reduced set
   run nccl "" allreduce "" "" float $AR_MIN $AR_MAX
-  for spec in "RING -" "PRD -" "PRM 2" "PRM $N" "K_RING 4"; do set -- $spec; k=$2; [ "$k" = "-" ] && k=""; run ours-$1-k${k:--1} $OURS allreduce $1 "$k" float $AR_MIN $AR_MAX; done
+  for spec in "RING -" "PRD -" "PRM 2" "PRM $N" "K_RING 4" "DIRECT -"; do set -- $spec; k=$2; [ "$k" = "-" ] && k=""; run ours-$1-k${k:--1} $OURS allreduce $1 "$k" float $AR_MIN $AR_MAX; done
   if [ -f $REF ]; then run ref-RING $REF allreduce RING "" float $AR_MIN $AR_MAX; run ref-PRD $REF allreduce PRD "" float $AR_MIN $AR_MAX; run ref-PRM-k$N $REF allreduce PRM $N float $AR_MIN $AR_MAX; fi
   run nccl "" allreduce "" "" bf16 $AR_MIN $AR_MAX
-  for spec in "RING -" "PRD -" "PRM $N"; do set -- $spec; k=$2; [ "$k" = "-" ] && k=""; run ours-$1-k${k:--1} $OURS allreduce $1 "$k" bf16 $AR_MIN $AR_MAX; done
+  for spec in "RING -" "PRD -" "PRM $N" "DIRECT -"; do set -- $spec; k=$2; [ "$k" = "-" ] && k=""; run ours-$1-k${k:--1} $OURS allreduce $1 "$k" bf16 $AR_MIN $AR_MAX; done
   for coll in allgather reduce_scatter reduce broadcast; do
     run nccl "" $coll "" "" float 1024 $BLK_MAX
     run ours-RING-k-1 $OURS $coll RING "" float 1024 $BLK_MAX
     run ours-PRD-k-1 $OURS $coll PRD "" float 1024 $BLK_MAX
     run ours-PRM-k2 $OURS $coll PRM 2 float 1024 $BLK_MAX
+    run ours-DIRECT-k-1 $OURS $coll DIRECT "" float 1024 $BLK_MAX
     run nccl "" $coll "" "" bf16 1024 $BLK_MAX
     run ours-RING-k-1 $OURS $coll RING "" bf16 1024 $BLK_MAX
   done
@@ -49,6 +50,7 @@ for dt in float bf16; do
   run nccl "" allreduce "" "" $dt 8 $AR_MAX
   run ours-RING-k-1 $OURS allreduce RING "" $dt 8 $AR_MAX
   run ours-PRD-k-1 $OURS allreduce PRD "" $dt 8 $AR_MAX
+  run ours-DIRECT-k-1 $OURS allreduce DIRECT "" $dt 8 $AR_MAX
   for k in $KS; do run ours-PRM-k$k $OURS allreduce PRM $k $dt 8 $AR_MAX; done
   for k in 2 4; do [ $((N % k)) -eq 0 ] && [ $k -lt $N ] && run ours-K_RING-k$k $OURS allreduce K_RING $k $dt 8 $AR_MAX; done
 done
@@ -65,6 +67,7 @@ for coll in allgather reduce_scatter reduce broadcast; do
     run ours-RING-k-1 $OURS $coll RING "" $dt 1024 $BLK_MAX
     run ours-PRD-k-1 $OURS $coll PRD "" $dt 1024 $BLK_MAX
     run ours-PRM-k2 $OURS $coll PRM 2 $dt 1024 $BLK_MAX
+    run ours-DIRECT-k-1 $OURS $coll DIRECT "" $dt 1024 $BLK_MAX
     [ $((N % 2)) -eq 0 ] && [ 2 -lt $N ] && run ours-K_RING-k2 $OURS $coll K_RING 2 $dt 1024 $BLK_MAX
   done
 done

@@ -12,7 +12,7 @@ _libs: dict[str, C.CDLL] = {}
 
 # numeric values shared with src/include/piccl.h
 COLL = {"allgather": 0, "allreduce": 1, "broadcast": 2, "reduce": 3, "reduce_scatter": 4}
-ALGO = {"DEFAULT": 0, "RING": 1, "K_RING": 2, "RD": 3, "RM": 4, "PRD": 5, "PRM": 6, "AUTO": 7}
+ALGO = {"DEFAULT": 0, "RING": 1, "K_RING": 2, "RD": 3, "RM": 4, "PRD": 5, "PRM": 6, "AUTO": 7, "DIRECT": 8, "NVLS": 9}
 OP = {"sum": 0, "prod": 1, "max": 2, "min": 3, "avg": 4}
 # ncclDataType_t numbering
 DTYPE = {"int8": 0, "uint8": 1, "int32": 2, "uint32": 3, "int64": 4, "uint64": 5, "float16": 6, "float32": 7, "float64": 8, "bfloat16": 9}
@@ -35,7 +35,7 @@ class Status(C.Structure):
 class Stats(C.Structure):
     _fields_ = [("calls", C.c_ulonglong * 5), ("bytes", C.c_ulonglong * 5), ("launches", C.c_ulonglong),
                 ("program_cache_hits", C.c_ulonglong), ("program_cache_misses", C.c_ulonglong),
-                ("fallbacks", C.c_ulonglong), ("timeouts", C.c_ulonglong), ("persistent_calls", C.c_ulonglong)]
+                ("fallbacks", C.c_ulonglong), ("timeouts", C.c_ulonglong), ("persistent_calls", C.c_ulonglong), ("nvls_calls", C.c_ulonglong)]
 
 
 def _ensure_built(name: str) -> Path:

@@ -66,8 +66,28 @@ static Program ar_recursive(const CollArgs& a, const Resolved& rs, int rank, boo
   return b.finish();
 }
 
+// DIRECT: every rank owns one chunk.  Step 0 hands each owner my contribution to its chunk, step 1
+// reduces my chunk (the peers' contributions and mine, in rank order) and sends the sum to everybody
+// while it is stored, step 2 stores the peers' sums.  Per rank 2(n-1)/n of the vector crosses the
+// switch, as with the ring, but in three steps.
+static Program ar_direct(const CollArgs& a, int rank) {
+  int n = a.nranks;
+  Builder b(rank, n);
+  std::vector<int64_t> displ, cnt; ar_chunks(a.count, n, a.elem_size, displ, cnt);
+  std::vector<int> others;
+  for (int j = 1; j < n; j++) others.push_back((rank + j) % n);
+  for (int p : others) b.act(BUF_IN, displ[p], BUF_NONE, 0, cnt[p], {}, {p});
+  b.next_step();
+  if (n > 1 || !a.in_place) b.act(BUF_IN, displ[rank], BUF_OUT, displ[rank], cnt[rank], others, others);
+  b.next_step();
+  for (int j = 1; j < n; j++) { int p = mod(rank - j, n); b.act(BUF_NONE, 0, BUF_OUT, displ[p], cnt[p], {p}, {}); }
+  b.next_step();
+  return b.finish();
+}
+
 Program compile_allreduce(const CollArgs& a, const Resolved& rs, int rank) {
   switch (rs.algo) {
+    case ALGO_DIRECT: return ar_direct(a, rank);
     case ALGO_K_RING: return ar_ring_like(a, rank, rs.k);
     case ALGO_RD: case ALGO_RM: return ar_recursive(a, rs, rank, false);
     case ALGO_PRD: case ALGO_PRM: return ar_recursive(a, rs, rank, true);

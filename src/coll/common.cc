@@ -10,8 +10,8 @@ const char* coll_name(Coll c) {
   return (c >= 0 && c < COLL_COUNT) ? n[c] : "?";
 }
 const char* algo_name(Algo a) {
-  static const char* n[] = {"DEFAULT", "RING", "K_RING", "RD", "RM", "PRD", "PRM", "AUTO"};
-  return (a >= 0 && a <= ALGO_AUTO) ? n[a] : "?";
+  static const char* n[] = {"DEFAULT", "RING", "K_RING", "RD", "RM", "PRD", "PRM", "AUTO", "DIRECT", "NVLS"};
+  return (a >= 0 && a <= ALGO_NVLS) ? n[a] : "?";
 }
 // Accepted spellings are the reference's (src/piccl.c:262-283) plus AUTO;
 // anything else selects the NCCL passthrough, as in the reference.
@@ -24,6 +24,8 @@ Algo algo_from_string(const char* s) {
   if (!strcmp(s, "PRD")) return ALGO_PRD;
   if (!strcmp(s, "PRM")) return ALGO_PRM;
   if (!strcmp(s, "AUTO")) return ALGO_AUTO;
+  if (!strcmp(s, "DIRECT")) return ALGO_DIRECT;
+  if (!strcmp(s, "NVLS")) return ALGO_NVLS;
   return ALGO_DEFAULT_NCCL;
 }
 
@@ -56,7 +58,14 @@ Resolved resolve(Coll coll, Algo algo, int k, int n) {
   if (algo == ALGO_DEFAULT_NCCL || algo == ALGO_AUTO) { r.algo = ALGO_RING; r.k = 0; r.note = "no algorithm given: RING"; return r; }
   if (n <= 1) { r.algo = ALGO_RING; r.k = 0; return r; }
   if (n > kMaxRanks) { r.algo = ALGO_RING; r.k = 0; r.note = "more ranks than supported by one action table"; return r; }
+  if (algo == ALGO_NVLS) { r.algo = ALGO_RING; r.k = 0; r.note = "NVLS is not a step schedule: RING"; return r; }
   if (algo == ALGO_RING) { r.k = 0; return r; }
+  if (algo == ALGO_DIRECT) {
+    if (n - 1 > kMaxActionPeers) { r.algo = ALGO_RING; r.k = 0; r.note = "DIRECT addresses at most 7 peers: RING"; return r; }
+    r.k = n;
+    if (coll == COLL_ALLGATHER || coll == COLL_REDUCE_SCATTER) { r.algo = ALGO_PRM; r.radices.assign(1, n); r.note = "DIRECT is PRM with k = n here"; }
+    return r;
+  }
   if (algo == ALGO_K_RING) {
     // The reference degrades to a plain ring when k does not divide n or k > n
     // (src/coll/allreduce.c:192-196); k unset (-1) is treated the same way.

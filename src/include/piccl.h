@@ -22,7 +22,9 @@ extern "C" {
 /* ---- enums (values shared with the schedule layer) ---- */
 enum { PICCL_ALLGATHER = 0, PICCL_ALLREDUCE = 1, PICCL_BROADCAST = 2, PICCL_REDUCE = 3, PICCL_REDUCE_SCATTER = 4 };
 enum { PICCL_ALGO_DEFAULT = 0, PICCL_ALGO_RING = 1, PICCL_ALGO_K_RING = 2, PICCL_ALGO_RD = 3, PICCL_ALGO_RM = 4,
-       PICCL_ALGO_PRD = 5, PICCL_ALGO_PRM = 6, PICCL_ALGO_AUTO = 7 };
+       PICCL_ALGO_PRD = 5, PICCL_ALGO_PRM = 6, PICCL_ALGO_AUTO = 7,
+       PICCL_ALGO_DIRECT = 8 /* every rank exchanges with every other rank at once; at most 8 ranks */,
+       PICCL_ALGO_NVLS = 9 /* all-reduce summed inside the NVSwitch; needs PICCL_NVLS=1, else runs RING */ };
 /* result codes: 0 ok; others mirror ncclResult_t */
 enum { PICCL_OK = 0, PICCL_CUDA_ERROR = 1, PICCL_SYSTEM_ERROR = 2, PICCL_INTERNAL_ERROR = 3, PICCL_INVALID_ARGUMENT = 4,
        PICCL_INVALID_USAGE = 5, PICCL_REMOTE_ERROR = 6, PICCL_UNSUPPORTED = 100 };
@@ -45,7 +47,8 @@ typedef struct { unsigned char bytes[128]; } piccl_handle_t;
 /* Device-reported status of the last failed wait (all zero while healthy). */
 typedef struct {
   int aborted;      /* 1 after a device-side wait ran out or piccl_comm_abort() */
-  int code;         /* 1: wait for FIFO credit, 2: wait for FIFO data, 3: aborted by host/peer CTA */
+  int code;         /* 1: wait for FIFO credit, 2: wait for FIFO data, 3: aborted by host/peer CTA,
+                       5 / 6: in-switch all-reduce, barrier before / after the reduction (segment = chunk) */
   int rank, cta, action, peer, segment;
   unsigned long long want, have;   /* counter value waited for / last seen */
 } piccl_status_t;
@@ -58,6 +61,7 @@ typedef struct {
   unsigned long long fallbacks;     /* calls the executor declined (reason logged with PICCL_LOG>=1) */
   unsigned long long timeouts;
   unsigned long long persistent_calls; /* calls served by the persistent launcher instead of a kernel launch */
+  unsigned long long nvls_calls;       /* all-reduces summed inside the switch */
 } piccl_stats_t;
 
 /* ---- communicator life cycle ----

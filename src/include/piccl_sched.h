@@ -21,8 +21,18 @@
 namespace piccl {
 
 enum Coll : int { COLL_ALLGATHER = 0, COLL_ALLREDUCE = 1, COLL_BROADCAST = 2, COLL_REDUCE = 3, COLL_REDUCE_SCATTER = 4, COLL_COUNT = 5 };
-// Same names as the reference's piccl_algo_t (src/include/piccl.h:13-21) plus AUTO.
-enum Algo : int { ALGO_DEFAULT_NCCL = 0, ALGO_RING = 1, ALGO_K_RING = 2, ALGO_RD = 3, ALGO_RM = 4, ALGO_PRD = 5, ALGO_PRM = 6, ALGO_AUTO = 7 };
+// Same names as the reference's piccl_algo_t (src/include/piccl.h:13-21) plus AUTO and DIRECT.
+// DIRECT has no counterpart in the reference: every rank talks to every other rank at once, which a
+// switch with full bandwidth between all pairs allows.  All-reduce: each rank owns 1/n of the vector,
+// one exchange delivers the contributions to the owners, a second one returns the sums (the ring's
+// traffic, 2(n-1)/n of the vector per rank, in 2 steps instead of 2(n-1)).  All-gather and
+// reduce-scatter: PRM with k = n.  Broadcast: the root scatters n slices, the ranks all-gather them.
+// Reduce: the ranks reduce-scatter n slices, the root gathers them.  At most 8 ranks (one action
+// addresses 7 peers); larger groups fall back to RING.
+// NVLS (all-reduce only, no counterpart either) is not a step schedule: the switch sums the contributions
+// (src/kernels/nvls.cuh).  The schedule layer treats it as RING, which is also what runs when a communicator
+// has no multicast window.
+enum Algo : int { ALGO_DEFAULT_NCCL = 0, ALGO_RING = 1, ALGO_K_RING = 2, ALGO_RD = 3, ALGO_RM = 4, ALGO_PRD = 5, ALGO_PRM = 6, ALGO_AUTO = 7, ALGO_DIRECT = 8, ALGO_NVLS = 9 };
 
 enum Buf : uint8_t { BUF_NONE = 0, BUF_IN = 1, BUF_OUT = 2, BUF_SCRATCH = 3 };
 
@@ -131,6 +141,6 @@ std::string dump_json(const CollArgs& a, int rank);
 
 const char* coll_name(Coll c);
 const char* algo_name(Algo a);
-Algo algo_from_string(const char* s);   // RING, K_RING, RD, RM, PRD, PRM, AUTO; else DEFAULT_NCCL
+Algo algo_from_string(const char* s);   // RING, K_RING, RD, RM, PRD, PRM, AUTO, DIRECT, NVLS; else DEFAULT_NCCL
 
 }  // namespace piccl

@@ -8,6 +8,7 @@
 // whatever the caller has (real NCCL in the preload shim, torch.distributed
 // in the Python package, a pipe in the benchmark).
 #include "comm.h"
+#include "nvls.h"
 #include <cuda_runtime.h>
 #include <nvtx3/nvToolsExt.h>
 #include <algorithm>
@@ -139,7 +140,8 @@ int piccl_comm_local_handle(piccl_comm_t* c, piccl_handle_t* out) {
   b.host_id = c->host_id; b.heap_bytes = (unsigned long long)c->heap_bytes; b.raw_ptr = (unsigned long long)(uintptr_t)c->heap;
   b.max_cta = c->cfg.max_cta; b.nslot = c->cfg.nslot; b.slot_bytes = (unsigned long long)c->cfg.slot_bytes;
   cudaError_t e = cudaIpcGetMemHandle(&b.ipc, c->heap);
-  b.ipc_ok = (e == cudaSuccess);
+  b.ipc_ok = (e == cudaSuccess) ? 1 : 0;
+  if (env().nvls && nvls_device_capable(c->device)) b.ipc_ok |= 2;
   if (e != cudaSuccess) { cudaGetLastError(); log_msg(1, "cudaIpcGetMemHandle: %s (peers in other processes cannot map this rank)", cudaGetErrorString(e)); }
   static_assert(sizeof(HandleBlob) <= sizeof(piccl_handle_t), "handle blob too large");
   memset(out, 0, sizeof *out); memcpy(out->bytes, &b, sizeof b);
@@ -168,7 +170,7 @@ int piccl_comm_connect(piccl_comm_t* c, const piccl_handle_t* all) {
       }
       c->h_ctx.heap[p] = (char*)(uintptr_t)b.raw_ptr;
     } else {
-      if (!b.ipc_ok) return fail(PICCL_UNSUPPORTED, "rank %d could not export its heap", p);
+      if (!(b.ipc_ok & 1)) return fail(PICCL_UNSUPPORTED, "rank %d could not export its heap", p);
       void* ptr = nullptr;
       cudaError_t e = cudaIpcOpenMemHandle(&ptr, b.ipc, cudaIpcMemLazyEnablePeerAccess);
       if (e != cudaSuccess) { cudaGetLastError(); return fail(PICCL_UNSUPPORTED, "cudaIpcOpenMemHandle(rank %d): %s", p, cudaGetErrorString(e)); }
@@ -177,6 +179,18 @@ int piccl_comm_connect(piccl_comm_t* c, const piccl_handle_t* all) {
   }
   CUDA_TRY(cudaMemcpy(c->d_ctx, &c->h_ctx, sizeof(RankCtx), cudaMemcpyHostToDevice));
   c->connected = true;
+  {
+    // In-switch all-reduce: only if every rank asked for it and can do it, and no two ranks share a process
+    // (each rank binds its own device to the multicast object, and the set-up blocks until all ranks take part).
+    bool want = true; int root_pid = 0; unsigned long long root_id = 0;
+    for (int p = 0; p < c->nranks; p++) {
+      HandleBlob b; memcpy(&b, all[p].bytes, sizeof b);
+      want &= (b.ipc_ok & 2) != 0;
+      if (p == 0) { root_pid = b.pid; root_id = b.raw_ptr; }
+      for (int q = 0; q < p; q++) { HandleBlob o; memcpy(&o, all[q].bytes, sizeof o); if (o.pid == b.pid) want = false; }
+    }
+    if (want) nvls_setup(c, root_pid, root_id);
+  }
   return PICCL_OK;
 }
 
@@ -185,6 +199,7 @@ int piccl_comm_destroy(piccl_comm_t* c) {
   DevGuard g(c->device);
   cudaDeviceSynchronize();
   persist_destroy(c);
+  nvls_destroy(c);
   if (!env().trace_file.empty()) trace_dump(c);
   if (env().log_level >= 1) {
     const piccl_stats_t& s = c->stats;
@@ -307,6 +322,7 @@ static int get_program(piccl_comm* c, const CollArgs& a, cudaStream_t stream, co
 static int choose_cta(const piccl_comm* c, const CollArgs& a, int n_vrank) {
   long long bytes = a.count * a.elem_size;
   if (a.coll == COLL_ALLREDUCE && (a.algo == ALGO_RING || a.algo == ALGO_K_RING)) bytes /= std::max(1, a.nranks);
+  if (a.algo == ALGO_DIRECT && a.coll != COLL_ALLGATHER && a.coll != COLL_REDUCE_SCATTER) bytes /= std::max(1, a.coll == COLL_ALLREDUCE ? a.nranks : a.nranks - 1);
   const Env& e = env();
   long long n = (bytes + 32767) / 32768;
   if (e.min_grid_set || e.max_grid_set) {
@@ -412,6 +428,18 @@ static int run(piccl_comm** comms, int n, const CallDesc* calls, cudaStream_t st
     }
   }
 
+  // all-reduce summed inside the switch (sum / avg of fp32, fp16, bf16; one communicator per launch); anything else runs the ring
+  if (d0.algo == ALGO_NVLS && d0.coll == COLL_ALLREDUCE && n == 1 && op == 0 && nvls_ready(c0) && nvls_dtype_supported(d0.dtype)) {
+    std::lock_guard<std::mutex> l(c0->mu);
+    const bool skip = fault_now(c0); c0->call_index++;
+    if (skip) return PICCL_OK;
+    TraceRec* tr = trace_begin(c0, d0.coll, d0.algo, 0, (long long)d0.count * esz_real, 0, stream);
+    int rc = nvls_allreduce(c0, d0.send, d0.recv, d0.count, d0.dtype, avg, stream);
+    trace_end(c0, tr, stream);
+    if (rc == PICCL_OK) { c0->stats.launches++; c0->stats.nvls_calls++; c0->stats.calls[COLL_ALLREDUCE]++; c0->stats.bytes[COLL_ALLREDUCE] += (unsigned long long)d0.count * esz_real; }
+    return rc;
+  }
+
   // slabs: bound the local scratch of the recursive reduce-scatters
   long long slab = count, stride = 0;
   if (d0.coll == COLL_REDUCE_SCATTER) {
@@ -450,6 +478,7 @@ static int run(piccl_comm** comms, int n, const CallDesc* calls, cudaStream_t st
         if (use_llf) {   // 4 KiB of payload per CTA and segment, at most kLLFifoCta CTAs
           long long ab = a.count * a.elem_size;
           if (a.coll == COLL_ALLREDUCE && (a.algo == ALGO_RING || a.algo == ALGO_K_RING)) ab /= std::max(1, a.nranks);
+          if (a.algo == ALGO_DIRECT && a.coll != COLL_ALLGATHER && a.coll != COLL_REDUCE_SCATTER) ab /= std::max(1, a.coll == COLL_ALLREDUCE ? a.nranks : a.nranks - 1);
           n_cta = (int)std::max<long long>(1, std::min<long long>((ab + 4095) / 4096, kLLFifoCta));
           if (n > 1) n_cta = std::min(n_cta, std::max(1, c->sm_count / n));
         }

@@ -15,7 +15,7 @@ namespace piccl {
 constexpr unsigned kHandleMagic = 0x5049434cu;   // "PICL"
 
 struct HandleBlob {
-  unsigned magic; int rank, nranks, pid, device; int max_cta, nslot, ipc_ok;
+  unsigned magic; int rank, nranks, pid, device; int max_cta, nslot, ipc_ok;   // ipc_ok bit 0: heap exported; bit 1: wants and can use an NVLink multicast window
   unsigned long long host_id, heap_bytes, raw_ptr, slot_bytes;
   cudaIpcMemHandle_t ipc;
 };
@@ -58,6 +58,7 @@ struct piccl_comm {
   unsigned tp_epoch_rs = 0, tp_epoch_ag = 0;   // epochs of the fused tensor-parallel kernels
   int* d_tp_status = nullptr;
   void* persist = nullptr;             // state of the persistent launcher (runtime/persistent.cu)
+  void* nvls = nullptr;                // multicast window of the in-switch all-reduce (runtime/nvls.cu)
   unsigned ll_epoch = 0;               // epoch of the last low-latency all-reduce (same on all ranks)
   long long ll_max_bytes = 0;          // largest message the low-latency path takes (0: off)
   piccl_stats_t stats{};

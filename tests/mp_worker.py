@@ -11,7 +11,7 @@ import torch.distributed as dist
 ROOT = Path(__file__).resolve().parent.parent
 sys.path.insert(0, str(ROOT))
 
-ALGOS = ["RING", "K_RING", "RD", "RM", "PRD", "PRM"]
+ALGOS = ["RING", "K_RING", "RD", "RM", "PRD", "PRM", "DIRECT"]
 
 
 def setup():
@@ -221,9 +221,39 @@ def case_tp(rank, world):
     comm.close()
 
 
+def case_nvls(rank, world):
+    """All-reduce summed inside the NVSwitch (PICCL_NVLS=1, algorithm NVLS) against NCCL."""
+    from piccl_b200.parallel.comm import Communicator, make_config
+    comm = Communicator(config=make_config(timeout_ms=20000))
+    probe = torch.ones(1024, device="cuda")
+    comm.all_reduce(probe, algo="NVLS")
+    torch.cuda.synchronize()
+    if comm.stats().nvls_calls == 0:
+        assert torch.equal(probe, torch.full_like(probe, float(world)))      # the ring ran instead
+        print("NVLS_UNAVAILABLE", flush=True)
+    else:
+        for dtype, count in [(torch.float32, 1), (torch.float32, 1000), (torch.bfloat16, (1 << 20) + 3), (torch.float16, 300001), (torch.float32, 48 << 20)]:
+            for op in ("sum", "avg"):
+                x = rand(count, dtype, 300 + rank)
+                want = x.clone()
+                dist.all_reduce(want, op=dist.ReduceOp.AVG if op == "avg" else dist.ReduceOp.SUM)
+                got = comm.all_reduce(x.clone(), op=op, algo="NVLS")
+                healthy(comm)
+                assert torch.allclose(got.float(), want.float(), atol=tol(dtype, world), rtol=1e-2), f"nvls {op} {dtype} {count}: {(got.float() - want.float()).abs().max().item()}"
+        # every rank ends with the same bits
+        x = rand(1 << 20, torch.bfloat16, 400 + rank)
+        got = comm.all_reduce(x, algo="NVLS")
+        ref = got.clone()
+        dist.broadcast(ref, 0)
+        assert torch.equal(got, ref)
+    dist.barrier()
+    comm.close()
+    print(f"WORKER_OK nvls", flush=True)
+
+
 if __name__ == "__main__":
     case = sys.argv[1]
     rank, world = setup()
-    {"collectives": case_collectives, "ddp": case_ddp, "shim": case_shim, "fault": case_fault, "tp": case_tp}[case](rank, world)
+    {"collectives": case_collectives, "ddp": case_ddp, "shim": case_shim, "fault": case_fault, "tp": case_tp, "nvls": case_nvls}[case](rank, world)
     print(f"WORKER_OK {case} rank {rank}", flush=True)
     dist.destroy_process_group()

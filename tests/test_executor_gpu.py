@@ -7,7 +7,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-ALGOS = ["RING", "K_RING", "RD", "RM", "PRD", "PRM"]
+ALGOS = ["RING", "K_RING", "RD", "RM", "PRD", "PRM", "DIRECT"]
 
 
 @pytest.fixture(scope="module")

@@ -10,7 +10,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 ROOT = Path(__file__).resolve().parent.parent
-ALGOS = ["RING", "K_RING", "RD", "RM", "PRD", "PRM"]
+ALGOS = ["RING", "K_RING", "RD", "RM", "PRD", "PRM", "DIRECT"]
 
 
 def _worker(rank, world, port, q):

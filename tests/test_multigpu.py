@@ -47,6 +47,12 @@ def test_fused_tensor_parallel_kernels():
     _run("tp")
 
 
+def test_in_switch_allreduce():
+    out = _run("nvls", {"PICCL_NVLS": "1", "PICCL_LOG": "1"})
+    if "NVLS_UNAVAILABLE" in out:
+        pytest.skip("no NVLink multicast window on this machine")
+
+
 def test_preload_shim_under_torch_distributed():
     from piccl_b200 import build
     so = str(build.lib_path("piccl.so"))

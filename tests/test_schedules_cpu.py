@@ -2,6 +2,7 @@
 (the reference ships no such test; its only check is the external OSU validation
 run, README.md:40-44)."""
 import itertools
+import json
 import xml.etree.ElementTree as ET
 
 import pytest
@@ -9,7 +10,7 @@ import pytest
 from piccl_b200 import schedule as S
 
 COLLS = ["allgather", "allreduce", "broadcast", "reduce", "reduce_scatter"]
-ALGOS = ["RING", "K_RING", "RD", "RM", "PRD", "PRM"]
+ALGOS = ["RING", "K_RING", "RD", "RM", "PRD", "PRM", "DIRECT"]
 
 
 @pytest.mark.parametrize("coll", COLLS)
@@ -59,6 +60,28 @@ def test_traffic_matches_cost_model():
     for algo in ALGOS:
         v = S.validate("allgather", algo, n, count, k=2, n_cta=1, seg_elems=count, elem_size=4)
         assert v.bytes_sent_max_rank == (n - 1) * S_bytes, algo
+
+
+def test_direct_schedules_move_the_minimum_in_two_exchanges():
+    n, count = 8, 7 * 8 * 1024
+    S_bytes = count * 4
+    # all-reduce: the ring's traffic in 3 steps (contributions out, reduce + sums out, sums stored)
+    v = S.validate("allreduce", "DIRECT", n, count, n_cta=1, seg_elems=count)
+    assert v.ok and v.bytes_sent_max_rank == 2 * (n - 1) * S_bytes // n
+    assert json.loads(S.schedule_json("allreduce", "DIRECT", n, count, 3))["steps"] == 3
+    prog = json.loads(S.schedule_json("allreduce", "DIRECT", n, count, 3))["actions"]
+    assert [len(a["send"]) for a in prog] == [1] * 7 + [7] + [0] * 7 and [len(a["recv"]) for a in prog] == [0] * 7 + [7] + [1] * 7
+    # broadcast: nobody sends more than the message, the root sends it exactly once
+    v = S.validate("broadcast", "DIRECT", n, count, root=5, n_cta=1, seg_elems=count)
+    assert v.ok and v.bytes_sent_max_rank == S_bytes
+    # reduce: each rank sends at most its vector once
+    v = S.validate("reduce", "DIRECT", n, count, root=2, n_cta=1, seg_elems=count)
+    assert v.ok and v.bytes_sent_max_rank == S_bytes
+    # all-gather / reduce-scatter resolve to one exchange with everybody
+    r = S.resolve("allgather", "DIRECT", -1, n)
+    assert (r.algo, r.k, r.radices) == ("PRM", 8, [8])
+    # more than 8 ranks: one action cannot address everybody
+    assert S.resolve("allreduce", "DIRECT", -1, 12).algo == "RING"
 
 
 def test_permutation_oracle_vectors():

@@ -60,3 +60,61 @@ def test_piccl_sched_cli():
     assert r.returncode == 0 and r.stdout.count("<transfer") == 7
     r = subprocess.run([str(tool), "json", "--collective", "allgather", "--algorithm", "PRD", "--nodes", "4", "--buffer-size", "4096", "--rank", "1"], capture_output=True, text=True)
     assert '"algorithm":"PRD"' in r.stdout
+
+
+# ---------------------------------------------------------------- descriptor hand-over between the ranks of one host
+def _fdshare_rank(rank, nranks, name, path, ok, timeout_ms, q):
+    import ctypes as C
+    import os
+    from piccl_b200 import _native as N
+    l = N.lib()
+    fd = os.open(path, os.O_RDONLY) if rank == 0 else -1
+    out, all_ok, err = C.c_int(-1), C.c_int(-1), C.create_string_buffer(256)
+    rc = l.piccl_fdshare_selftest(rank, nranks, name.encode(), fd, timeout_ms, int(ok), C.byref(out), C.byref(all_ok), err, 256)
+    text = None
+    if rc == 0 or out.value >= 0:
+        try:
+            text = os.pread(out.value, 64, 0).decode()
+        except OSError:
+            text = None
+    q.put((rank, rc, all_ok.value, text, err.value.decode()))
+
+
+def _run_fdshare(nranks, votes, tmp_path, timeout_ms=5000, absent=()):
+    import multiprocessing as mp
+    import os
+    ctx = mp.get_context("spawn")
+    path = tmp_path / "payload.txt"
+    path.write_text("descriptor payload")
+    name = f"piccl-test-{os.getpid()}-{nranks}-{len(absent)}-{sum(votes)}"
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_fdshare_rank, args=(r, nranks, name, str(path), votes[r], timeout_ms, q)) for r in range(nranks) if r not in absent]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=60) for _ in procs)
+    for p in procs:
+        p.join(30)
+    return res
+
+
+def test_fdshare_hands_the_descriptor_to_every_rank(tmp_path):
+    res = _run_fdshare(4, [True] * 4, tmp_path)
+    assert [r[0] for r in res] == [0, 1, 2, 3]
+    for rank, rc, all_ok, text, err in res:
+        assert rc == 0 and all_ok == 1 and text == "descriptor payload", (rank, rc, err)
+
+
+def test_fdshare_barrier_spreads_one_rank_failure(tmp_path):
+    res = _run_fdshare(3, [True, False, True], tmp_path)
+    for rank, rc, all_ok, text, err in res:
+        assert rc == 0 and all_ok == 0, (rank, rc, err)
+
+
+def test_fdshare_missing_rank_is_reported_within_the_limit(tmp_path):
+    import time
+    t0 = time.time()
+    res = _run_fdshare(3, [True] * 3, tmp_path, timeout_ms=1500, absent=(2,))
+    assert time.time() - t0 < 30
+    by_rank = {r[0]: r for r in res}
+    assert by_rank[0][1] == -1 and "timed out waiting for 1 peer" in by_rank[0][4]
+    assert by_rank[1][1] != 0          # rank 1 connected but never got a descriptor

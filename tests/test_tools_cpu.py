@@ -143,7 +143,7 @@ def test_selector_tables(tmp_path):
     assert select.main(["--profile", str(prof), "--ranks", "8", "--min", "8", "--max", str(1 << 28), "--output", str(out)]) == 0
     rows = [l.split(",") for l in out.read_text().splitlines() if not l.startswith("#")]
     ar = [r for r in rows if r[0] == "allreduce"]
-    assert ar[0][3] in ("PRM", "PRD") and ar[-1][3] in ("RING", "K_RING")       # latency-optimal first, bandwidth-optimal last
+    assert ar[0][3] in ("PRM", "PRD") and ar[-1][3] in ("RING", "K_RING", "DIRECT")       # latency-optimal first, bandwidth-optimal last
     assert int(ar[-1][2]) >= 1 << 60
     bench = tmp_path / "b.csv"
     bench.write_text("# coll,label,dtype,op,ranks,bytes,iters,time_us,algbw_GBs,busbw_GBs,check\n"

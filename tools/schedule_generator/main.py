@@ -23,7 +23,7 @@ from piccl_b200 import schedule as S  # noqa: E402
 
 COLLECTIVES = {"allgather": "allgather", "allreduce": "allreduce", "reduce": "reduce", "bcast": "broadcast", "broadcast": "broadcast",
                "reduce_scatter": "reduce_scatter"}
-ALGORITHMS = {"ring": "RING", "k_ring": "K_RING", "rd": "RD", "rm": "RM", "prd": "PRD", "prm": "PRM"}
+ALGORITHMS = {"ring": "RING", "k_ring": "K_RING", "rd": "RD", "rm": "RM", "prd": "PRD", "prm": "PRM", "direct": "DIRECT"}
 
 
 def generate(collective: str, num_nodes: int, buffer_size: int, algorithm: str = "ring", k: int = 1, root: int = 0) -> str:
@@ -44,7 +44,7 @@ def main(argv=None) -> int:
     ap.add_argument("--collective", type=str, required=True, help="allgather, allreduce, reduce, bcast, reduce_scatter")
     ap.add_argument("--num_nodes", type=int, required=True)
     ap.add_argument("--buffer_size", type=int, required=True, help="bytes of the whole buffer")
-    ap.add_argument("--algorithm", type=str, default="ring", help="ring, k_ring, RD, RM, PRD, PRM")
+    ap.add_argument("--algorithm", type=str, default="ring", help="ring, k_ring, RD, RM, PRD, PRM, direct")
     ap.add_argument("--k", type=int, default=1, help="group size (k_ring) or radix (RM, PRM)")
     ap.add_argument("--root", type=int, default=0)
     ap.add_argument("--output", type=str, required=True)

@@ -28,6 +28,8 @@ COLLS = ["allgather", "allreduce", "broadcast", "reduce", "reduce_scatter"]
 
 def candidates(n: int):
     out = [("RING", -1), ("PRD", -1)]
+    if 2 < n <= 8:
+        out.append(("DIRECT", -1))
     for k in (2, 4, 8):
         if 2 <= k <= n:
             out.append(("PRM", k))
