@@ -16,6 +16,8 @@
 //   3 ld_reduce the 1/n of the slot that this rank is responsible for, st the sums to all copies
 //   4 barrier
 //   5 copy the slot to the receive buffer
+// A pipelined variant (PICCL_NVLS_PIPE=1) splits the slot in two halves and overlaps the copy-in of the next chunk with
+// the switch phase of the current one; see the kernel.
 // Barrier counters only ever grow (n per barrier), over the life of the communicator.
 // Every poll is bounded: on a time-out the CTA records a status, raises the abort flag and leaves.
 #pragma once
@@ -24,8 +26,11 @@
 
 namespace piccl {
 
-constexpr int kNvlsFlagBytes = 65536;
-constexpr int kNvlsMaxCta = 256;          // kNvlsFlagBytes / 128 would allow 512
+constexpr int kNvlsFlagBytes = 131072;
+constexpr int kNvlsMaxCta = 256;          // counters of the plain kernel: [0, 32 KiB)
+constexpr int kNvlsPipeFlagOff = 32768;   // counters of the pipelined kernel: 4 per CTA index, [32 KiB, 96 KiB)
+constexpr int kNvlsPipeMaxCta = 128;
+constexpr int kNvlsBarCounts = kNvlsMaxCta + 2 * kNvlsPipeMaxCta;   // entries of NvlsArgs::bar_count
 constexpr int kNvlsBlock = 512;
 
 struct NvlsArgs {
@@ -35,9 +40,10 @@ struct NvlsArgs {
   long long chunk_bytes;                  // bytes of the message per chunk, multiple of 16 * nranks, <= slot_bytes
   long long slot_bytes;                   // distance between two slots of the window
   int rank, nranks, n_cta, avg;
+  int pipelined;                          // 0: one chunk in flight per CTA; 1: two half slots, copy-in overlapped with the switch phase (n_cta <= kNvlsPipeMaxCta)
   float scale;
   unsigned long long timeout_ns;
-  unsigned long long* bar_count;          // [kNvlsMaxCta] barriers passed so far per CTA index (device memory)
+  unsigned long long* bar_count;          // [kNvlsBarCounts] device memory: barriers passed per CTA index (plain kernel), then uses of each half slot (pipelined)
   int* abort_flag;
   piccl_status_t* status;
 };

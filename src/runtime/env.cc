@@ -43,6 +43,7 @@ static void load() {
   e.nvls = env_int("PICCL_NVLS", 0);            // 1: build an NVLink multicast window per communicator (algorithm NVLS)
   e.nvls_chunk_kb = env_int("PICCL_NVLS_CHUNK_KB", 256);
   e.nvls_cta = env_int("PICCL_NVLS_CTA", 64);
+  e.nvls_pipe = env_int("PICCL_NVLS_PIPE", 0);   // 1: the pipelined kernel (two half slots per CTA)
   e.log_level = env_int("PICCL_LOG", 0);
   e.debug = env_int("PICCL_DEBUG", 0);
   { const char* l = getenv("PICCL_LAUNCH"); e.launch_persistent = l && !strcmp(l, "persistent"); }

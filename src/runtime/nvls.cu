@@ -203,8 +203,8 @@ void nvls_setup(piccl_comm* c, int root_pid, unsigned long long root_id) {
 #undef STEP
   if (ok) {
     cudaError_t ce = cudaMemset((void*)s->uc_va, 0, kNvlsFlagBytes);
-    if (ce == cudaSuccess) ce = cudaMalloc(&s->d_bar, kNvlsMaxCta * sizeof(unsigned long long));
-    if (ce == cudaSuccess) ce = cudaMemset(s->d_bar, 0, kNvlsMaxCta * sizeof(unsigned long long));
+    if (ce == cudaSuccess) ce = cudaMalloc(&s->d_bar, kNvlsBarCounts * sizeof(unsigned long long));
+    if (ce == cudaSuccess) ce = cudaMemset(s->d_bar, 0, kNvlsBarCounts * sizeof(unsigned long long));
     if (ce == cudaSuccess) ce = cudaDeviceSynchronize();
     if (ce != cudaSuccess) { cudaGetLastError(); ok = false; snprintf(why, sizeof why, "clearing the window: %s", cudaGetErrorString(ce)); }
   }
@@ -232,10 +232,14 @@ int nvls_allreduce(piccl_comm* c, const void* in, void* out, size_t count, int d
   long long chunk = (bytes + s->max_cta - 1) / s->max_cta;
   chunk = std::max<long long>(chunk, 16384);
   chunk = (chunk + unit - 1) / unit * unit;
-  a.chunk_bytes = std::min(chunk, s->slot_bytes);
+  a.pipelined = env().nvls_pipe ? 1 : 0;
+  const int max_cta = a.pipelined ? std::min(s->max_cta, kNvlsPipeMaxCta) : s->max_cta;
+  const long long room = a.pipelined ? (s->slot_bytes / 2) / unit * unit : s->slot_bytes;      // a chunk fills a slot, or half of it
+  if (room < unit) return PICCL_UNSUPPORTED;
+  a.chunk_bytes = std::min(chunk, room);
   a.slot_bytes = s->slot_bytes;
   const long long nchunks = (bytes + a.chunk_bytes - 1) / a.chunk_bytes;
-  a.rank = c->rank; a.nranks = c->nranks; a.n_cta = (int)std::min<long long>(nchunks, s->max_cta);
+  a.rank = c->rank; a.nranks = c->nranks; a.n_cta = (int)std::min<long long>(nchunks, max_cta);
   a.avg = avg ? 1 : 0; a.scale = avg ? 1.0f / (float)c->nranks : 1.0f;
   a.timeout_ns = (unsigned long long)c->cfg.timeout_ms * 1000000ull;
   a.bar_count = s->d_bar; a.abort_flag = c->d_abort; a.status = c->d_status;

@@ -47,8 +47,9 @@ def test_fused_tensor_parallel_kernels():
     _run("tp")
 
 
-def test_in_switch_allreduce():
-    out = _run("nvls", {"PICCL_NVLS": "1", "PICCL_LOG": "1"})
+@pytest.mark.parametrize("pipelined", ["0", "1"])
+def test_in_switch_allreduce(pipelined):
+    out = _run("nvls", {"PICCL_NVLS": "1", "PICCL_NVLS_PIPE": pipelined, "PICCL_LOG": "1"})
     if "NVLS_UNAVAILABLE" in out:
         pytest.skip("no NVLink multicast window on this machine")
 
