@@ -26,7 +26,9 @@ long long piccl_sched_json(int coll, int algo, int k, int n, int root, long long
 }
 int piccl_sched_resolve(int coll, int algo, int k, int n, int* out_algo, int* out_k, int* radices, int* n_radices, int* core, char* note, int note_cap) {
   Resolved r = resolve((Coll)coll, (Algo)algo, k, n);
-  if (out_algo) *out_algo = r.algo; if (out_k) *out_k = r.k; if (core) *core = r.core;
+  if (out_algo) *out_algo = r.algo;
+  if (out_k) *out_k = r.k;
+  if (core) *core = r.core;
   if (n_radices) { int m = (int)r.radices.size(); if (radices) for (int i = 0; i < m && i < *n_radices; i++) radices[i] = r.radices[i]; *n_radices = m; }
   put(r.note, note, note_cap);
   return 0;
@@ -36,14 +38,18 @@ int piccl_sched_validate(int coll, int algo, int k, int n, int root, long long c
                          long long* fifo_entries, int* max_depth, double* max_err, long long* bytes_sent, char* err, int err_cap) {
   CollArgs a = mk(coll, algo, k, n, root, count, stride, esz, in_place);
   ValidateResult v = symbolic ? validate_symbolic(a, fifo_cap, n_cta) : validate(a, op, integer != 0, fifo_cap, seg_elems, n_cta);
-  if (fifo_entries) *fifo_entries = v.fifo_entries; if (max_depth) *max_depth = v.max_fifo_depth;
-  if (max_err) *max_err = v.max_abs_err; if (bytes_sent) *bytes_sent = v.bytes_sent_max_rank;
+  if (fifo_entries) *fifo_entries = v.fifo_entries;
+  if (max_depth) *max_depth = v.max_fifo_depth;
+  if (max_err) *max_err = v.max_abs_err;
+  if (bytes_sent) *bytes_sent = v.bytes_sent_max_rank;
   put(v.error, err, err_cap);
   return v.ok ? 0 : 1;
 }
 int piccl_permutation_index(int r, int n, int b, int* out) {
-  std::vector<int> p; if (!permutation_index(r, n, b, p)) return 1;
-  for (int i = 0; i < n; i++) out[i] = p[i]; return 0;
+  std::vector<int> p;
+  if (!permutation_index(r, n, b, p)) return 1;
+  for (int i = 0; i < n; i++) out[i] = p[i];
+  return 0;
 }
 int piccl_held_blocks(int r, int s, const int* radices, int n_radices, int n, int permuted, int* out) {
   std::vector<int> rd(radices, radices + n_radices);
@@ -53,7 +59,9 @@ int piccl_held_blocks(int r, int s, const int* radices, int n_radices, int n, in
 }
 int piccl_sched_counts(int coll, int algo, int k, int n, int root, long long count, int esz, int rank, int* n_actions, int* n_steps, long long* scratch_elems) {
   Program p = compile(mk(coll, algo, k, n, root, count, 0, esz, 0), rank);
-  if (n_actions) *n_actions = (int)p.actions.size(); if (n_steps) *n_steps = p.nsteps; if (scratch_elems) *scratch_elems = p.scratch_elems;
+  if (n_actions) *n_actions = (int)p.actions.size();
+  if (n_steps) *n_steps = p.nsteps;
+  if (scratch_elems) *scratch_elems = p.scratch_elems;
   return 0;
 }
 

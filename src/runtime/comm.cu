@@ -429,7 +429,7 @@ static int run(piccl_comm** comms, int n, const CallDesc* calls, cudaStream_t st
   }
 
   // all-reduce summed inside the switch (sum / avg of fp32, fp16, bf16; one communicator per launch); anything else runs the ring
-  if (d0.algo == ALGO_NVLS && d0.coll == COLL_ALLREDUCE && n == 1 && op == 0 && nvls_ready(c0) && nvls_dtype_supported(d0.dtype)) {
+  if ((d0.algo == ALGO_NVLS || env().proto == 3) && d0.coll == COLL_ALLREDUCE && n == 1 && op == 0 && nvls_ready(c0) && nvls_dtype_supported(d0.dtype)) {
     std::lock_guard<std::mutex> l(c0->mu);
     const bool skip = fault_now(c0); c0->call_index++;
     if (skip) return PICCL_OK;

@@ -1,4 +1,5 @@
 #include "env.h"
+#include <algorithm>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -44,6 +45,17 @@ static void load() {
   e.nvls_chunk_kb = env_int("PICCL_NVLS_CHUNK_KB", 256);
   e.nvls_cta = env_int("PICCL_NVLS_CTA", 64);
   e.nvls_pipe = env_int("PICCL_NVLS_PIPE", 0);   // 1: the pipelined kernel (two half slots per CTA)
+  // PICCL_PROTO narrows the choice of data path that is otherwise made per call by message size:
+  //   auto    (default) low-latency kernels for small messages, the FIFO executor otherwise
+  //   simple  FIFO executor only
+  //   ll      low-latency executor up to 1 MiB for every collective
+  //   nvls    builds the multicast window and sums every eligible all-reduce (sum / avg of fp32, fp16, bf16) inside the switch
+  e.proto = 0;
+  if (const char* p = getenv("PICCL_PROTO")) {
+    if (!strcmp(p, "ll")) { e.proto = 1; e.llf_kb = std::max(e.llf_kb, 1024); }
+    else if (!strcmp(p, "simple")) { e.proto = 2; e.ll_kb = 0; e.llf_kb = 0; }
+    else if (!strcmp(p, "nvls")) { e.proto = 3; e.nvls = 1; }
+  }
   e.log_level = env_int("PICCL_LOG", 0);
   e.debug = env_int("PICCL_DEBUG", 0);
   { const char* l = getenv("PICCL_LAUNCH"); e.launch_persistent = l && !strcmp(l, "persistent"); }
@@ -73,3 +85,17 @@ void log_msg(int level, const char* fmt, ...) {
 }
 
 }  // namespace piccl
+
+// The effective configuration as "key=value" pairs separated by blanks (for logs and tests).
+// Returns the length needed, like snprintf.
+extern "C" int piccl_env_describe(char* buf, int len) {
+  const piccl::Env& e = piccl::env();
+  static const char* proto[] = {"auto", "ll", "simple", "nvls"};
+  return snprintf(buf, len > 0 ? (size_t)len : 0,
+                  "proto=%s ll_kb=%d llf_kb=%d nvls=%d nvls_chunk_kb=%d nvls_cta=%d nvls_pipe=%d max_cta=%d slot_kb=%d nslot=%d timeout_ms=%d "
+                  "launch=%s allreduce=%s/%d allgather=%s/%d broadcast=%s/%d reduce=%s/%d reduce_scatter=%s/%d",
+                  proto[e.proto & 3], e.ll_kb, e.llf_kb, e.nvls, e.nvls_chunk_kb, e.nvls_cta, e.nvls_pipe, e.max_cta, e.slot_kb, e.nslot, e.timeout_ms,
+                  e.launch_persistent ? "persistent" : "direct", piccl::algo_name(e.algo[piccl::COLL_ALLREDUCE]), e.k[piccl::COLL_ALLREDUCE],
+                  piccl::algo_name(e.algo[piccl::COLL_ALLGATHER]), e.k[piccl::COLL_ALLGATHER], piccl::algo_name(e.algo[piccl::COLL_BROADCAST]), e.k[piccl::COLL_BROADCAST],
+                  piccl::algo_name(e.algo[piccl::COLL_REDUCE]), e.k[piccl::COLL_REDUCE], piccl::algo_name(e.algo[piccl::COLL_REDUCE_SCATTER]), e.k[piccl::COLL_REDUCE_SCATTER]);
+}

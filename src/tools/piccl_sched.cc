@@ -31,7 +31,8 @@ static Algo algo_from(std::string s) {
 int main(int argc, char** argv) {
   if (argc < 2) { fprintf(stderr, "usage: piccl_sched xml|json|validate --collective C --algorithm A [--k K] --nodes N --buffer-size B\n"); return 2; }
   std::string cmd = argv[1];
-  CollArgs a; a.elem_size = 4; int rank = 0, op = 0, fifo = 1, cta = 1; bool integer = false, symbolic = false; int64_t seg = 0, bytes = 0;
+  // fifo = 2: the smallest FIFO depth the runtime allows (a fused receive + forward needs two entries in flight)
+  CollArgs a; a.elem_size = 4; int rank = 0, op = 0, fifo = 2, cta = 1; bool integer = false, symbolic = false; int64_t seg = 0, bytes = 0;
   for (int i = 2; i < argc; i++) {
     std::string f = argv[i];
     auto val = [&]() -> const char* { if (i + 1 >= argc) { fprintf(stderr, "missing value for %s\n", f.c_str()); exit(2); } return argv[++i]; };

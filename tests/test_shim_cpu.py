@@ -40,11 +40,33 @@ def test_algorithm_names_are_the_reference_names():
     sys.path.insert(0, str(ROOT))
     from piccl_b200 import _native as N
     lib = N.lib()
-    names = {"RING": 1, "K_RING": 2, "RD": 3, "RM": 4, "PRD": 5, "PRM": 6, "AUTO": 7}
+    names = {"RING": 1, "K_RING": 2, "RD": 3, "RM": 4, "PRD": 5, "PRM": 6, "AUTO": 7, "DIRECT": 8, "NVLS": 9}
     for k, v in names.items():
         assert lib.piccl_algo_from_string(k.encode()) == v
     for bad in [b"ring", b"", b"NCCL", b"DEFAULT"]:
         assert lib.piccl_algo_from_string(bad) == 0               # anything else: passthrough
+
+
+def test_protocol_switch_and_effective_configuration():
+    """PICCL_PROTO narrows the per-call choice of data path; piccl_env_describe reports what is in force."""
+    code = ("import ctypes as C, sys; sys.path.insert(0, %r); from piccl_b200 import _native as N; l = N.lib(); "
+            "b = C.create_string_buffer(1024); l.piccl_env_describe(b, 1024); print(b.value.decode())") % str(ROOT)
+
+    def describe(**env):
+        e = dict(os.environ); e.update(env)
+        out = subprocess.run([sys.executable, "-c", code], env=e, capture_output=True, text=True, check=True).stdout.strip().splitlines()[-1]
+        return dict(kv.split("=", 1) for kv in out.split())
+
+    d = describe()
+    assert d["proto"] == "auto" and d["ll_kb"] == "1024" and d["llf_kb"] == "64" and d["nvls"] == "0" and d["allreduce"] == "DEFAULT/-1"
+    d = describe(PICCL_PROTO="simple")
+    assert d["proto"] == "simple" and d["ll_kb"] == "0" and d["llf_kb"] == "0"
+    d = describe(PICCL_PROTO="ll")
+    assert d["proto"] == "ll" and d["llf_kb"] == "1024"
+    d = describe(PICCL_PROTO="nvls", PICCL_ALLREDUCE_ALGO="DIRECT", PICCL_ALLGATHER_ALGO="PRM", PICCL_ALLGATHER_K="4", PICCL_NVLS_PIPE="1")
+    assert d["proto"] == "nvls" and d["nvls"] == "1" and d["nvls_pipe"] == "1" and d["allreduce"] == "DIRECT/-1" and d["allgather"] == "PRM/4"
+    d = describe(PICCL_PROTO="bogus")
+    assert d["proto"] == "auto"
 
 
 def test_piccl_sched_cli():
