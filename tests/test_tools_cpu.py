@@ -215,3 +215,21 @@ def test_standalone_k_ring_generator(tmp_path):
     import json
     rec = json.loads(out.strip().splitlines()[-1])
     assert rec["rank"] == 1 and len(rec["sends"]) == 3 and len(rec["recvs"]) == 3
+
+
+def test_shipped_samples_simulate(tmp_path):
+    """Sample schedules, topologies and profiles under tools/loggp_sim (reference: tools/loggp_sim/schedules, profiles)."""
+    sim = ROOT / "tools" / "loggp_sim"
+
+    def run(sched, topo, radix=1):
+        out = subprocess.run([sys.executable, str(sim / "sim.py"), "--schedule", str(sim / "schedules" / sched), "--topo", str(sim / "topo" / topo), "--radix", str(radix)],
+                             capture_output=True, text=True, check=True, cwd=tmp_path).stdout
+        return float(out.strip().splitlines()[-1])
+
+    ring, k2, direct = run("8_ring_allgather.xml", "8_flat.xml"), run("8_kring_k_2_allgather.xml", "8_flat.xml"), run("8_direct_allgather.xml", "8_flat.xml")
+    assert ring == pytest.approx(k2) and direct < ring                 # one switch: group size does not matter, fewer steps do
+    flat_ring, flat_k8 = run("16_ring_allreduce.xml", "2x8_two_level.xml"), run("16_kring_k_8_allreduce.xml", "2x8_two_level.xml")
+    assert flat_k8 < flat_ring                                         # two nodes: keeping most hops inside a node pays
+    # the samples are what the generator writes today
+    assert (sim / "schedules" / "8_direct_allreduce.xml").read_text() == gen.generate("allreduce", 8, 1 << 24, "direct", 1)
+    assert (sim / "schedules" / "8_ring_allgather.xml").read_text() == gen.generate("allgather", 8, 8 * 4097, "ring", 1)
