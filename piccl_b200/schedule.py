@@ -71,13 +71,14 @@ class Validation:
 
 def validate(coll, algo, nranks: int, count: int, k: int = -1, root: int = 0, elem_size: int = 4, in_place: bool = False,
              op: str = "sum", integer: bool = False, fifo_cap: int = 2, seg_elems: int = 64, n_cta: int = 2,
-             stride: int = 0, symbolic: bool = False) -> Validation:
-    """Runs all ranks' programs against each other on the CPU (see src/coll/validate.cc)."""
+             stride: int = 0, symbolic: bool = False, deferred: bool = False) -> Validation:
+    """Runs all ranks' programs against each other on the CPU (see src/coll/validate.cc).
+    `deferred` models the executor variant that publishes its FIFO counters only when it is about to block."""
     l = N.lib()
     ent, depth, err, sent = C.c_longlong(), C.c_int(), C.c_double(), C.c_longlong()
     msg = C.create_string_buffer(512)
     rc = l.piccl_sched_validate(_coll(coll), _algo(algo), k, nranks, root, count, stride, elem_size, int(in_place), N.OP[op], int(integer),
-                                fifo_cap, seg_elems, n_cta, int(symbolic), C.byref(ent), C.byref(depth), C.byref(err), C.byref(sent), msg, 512)
+                                fifo_cap, seg_elems, n_cta, int(symbolic) | (2 if deferred else 0), C.byref(ent), C.byref(depth), C.byref(err), C.byref(sent), msg, 512)
     return Validation(rc == 0, msg.value.decode(), ent.value, depth.value, err.value, sent.value)
 
 

@@ -37,7 +37,9 @@ int piccl_sched_validate(int coll, int algo, int k, int n, int root, long long c
                          int op, int integer, int fifo_cap, long long seg_elems, int n_cta, int symbolic,
                          long long* fifo_entries, int* max_depth, double* max_err, long long* bytes_sent, char* err, int err_cap) {
   CollArgs a = mk(coll, algo, k, n, root, count, stride, esz, in_place);
-  ValidateResult v = symbolic ? validate_symbolic(a, fifo_cap, n_cta) : validate(a, op, integer != 0, fifo_cap, seg_elems, n_cta);
+  // `symbolic`: bit 0 = no data (coverage and FIFO order only), bit 1 = deferred publishing of the counters
+  const bool defer = (symbolic & 2) != 0;
+  ValidateResult v = (symbolic & 1) ? validate_symbolic(a, fifo_cap, n_cta, defer) : validate(a, op, integer != 0, fifo_cap, seg_elems, n_cta, defer);
   if (fifo_entries) *fifo_entries = v.fifo_entries;
   if (max_depth) *max_depth = v.max_fifo_depth;
   if (max_err) *max_err = v.max_abs_err;

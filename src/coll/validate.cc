@@ -31,7 +31,7 @@ Sizes buffer_sizes(const CollArgs& a) {
 }
 
 template <class T>
-ValidateResult run(const CollArgs& a, int op, bool with_data, int fifo_cap, int64_t seg_elems_req, int n_cta) {
+ValidateResult run(const CollArgs& a, int op, bool with_data, int fifo_cap, int64_t seg_elems_req, int n_cta, bool defer) {
   ValidateResult res;
   int n = a.nranks;
   int64_t st = a.block_stride ? a.block_stride : a.count;
@@ -77,6 +77,18 @@ ValidateResult run(const CollArgs& a, int op, bool with_data, int fifo_cap, int6
     struct Entry { std::vector<T> data; int64_t n; };
     std::vector<std::deque<Entry>> fifo((size_t)n * n);   // [src*n+dst]
     std::vector<Cursor> cur(n);
+    // Deferred publishing (the executor's DEFER variant): a push is visible to the consumer, and a pop to the producer, only
+    // once the rank that made it has published it, which it does when it is about to block and when its program ends.
+    std::vector<int64_t> pushed((size_t)n * n, 0), popped((size_t)n * n, 0), pub_push((size_t)n * n, 0), pub_pop((size_t)n * n, 0);
+    auto flush = [&](int r) {
+      bool any = false;
+      for (int o = 0; o < n; o++) {
+        size_t out_c = (size_t)r * n + o, in_c = (size_t)o * n + r;
+        if (pub_push[out_c] != pushed[out_c]) { pub_push[out_c] = pushed[out_c]; any = true; }
+        if (pub_pop[in_c] != popped[in_c]) { pub_pop[in_c] = popped[in_c]; any = true; }
+      }
+      return any;
+    };
     // device order: outer loop over segments, inner loop over all actions of the program
     for (int r = 0; r < n; r++) {
       for (auto& ac : progs[r].actions) cur[r].maxseg = std::max(cur[r].maxseg, slice_of(ac.count, a.elem_size, cta, n_cta, slot_bytes).nseg);
@@ -99,9 +111,15 @@ ValidateResult run(const CollArgs& a, int op, bool with_data, int fifo_cap, int6
           bool advance = true;
           if (c.seg < sl.nseg) {
             bool ready = true;
-            for (int i = 0; i < ac.n_send; i++) if ((int)fifo[(size_t)r * n + ac.send_peer[i]].size() >= fifo_cap) ready = false;
-            for (int i = 0; i < ac.n_recv; i++) if (fifo[(size_t)ac.recv_peer[i] * n + r].empty()) ready = false;
-            if (!ready) { advance = false; }
+            for (int i = 0; i < ac.n_send; i++) {
+              size_t cn = (size_t)r * n + ac.send_peer[i];
+              if ((defer ? pushed[cn] - pub_pop[cn] : (int64_t)fifo[cn].size()) >= fifo_cap) ready = false;
+            }
+            for (int i = 0; i < ac.n_recv; i++) {
+              size_t cn = (size_t)ac.recv_peer[i] * n + r;
+              if (defer ? pub_push[cn] - popped[cn] <= 0 : fifo[cn].empty()) ready = false;
+            }
+            if (!ready) { advance = false; if (defer && flush(r)) progress = true; }
             else {
               int64_t lo = sl.lo + (int64_t)c.seg * sl.seg_elems, hi = std::min(sl.hi, lo + sl.seg_elems), len = hi - lo;
               std::vector<T> val;
@@ -124,7 +142,7 @@ ValidateResult run(const CollArgs& a, int op, bool with_data, int fifo_cap, int6
               } else {
                 for (int i = 0; i < ac.n_recv; i++) if (fifo[(size_t)ac.recv_peer[i] * n + r].front().n != len) { res.error = "fifo entry size mismatch"; return res; }
               }
-              for (int i = 0; i < ac.n_recv; i++) fifo[(size_t)ac.recv_peer[i] * n + r].pop_front();
+              for (int i = 0; i < ac.n_recv; i++) { fifo[(size_t)ac.recv_peer[i] * n + r].pop_front(); popped[(size_t)ac.recv_peer[i] * n + r]++; }
               if (ac.dst_buf != BUF_NONE) {
                 int64_t lim = ac.dst_buf == BUF_OUT ? sz.out_elems : p.scratch_elems;
                 if (ac.dst_buf == BUF_IN || ac.dst_off + hi > lim || ac.dst_off + lo < 0) { res.error = "destination range out of bounds"; return res; }
@@ -133,7 +151,7 @@ ValidateResult run(const CollArgs& a, int op, bool with_data, int fifo_cap, int6
               }
               for (int i = 0; i < ac.n_send; i++) {
                 auto& q = fifo[(size_t)r * n + ac.send_peer[i]];
-                q.push_back(Entry{val, len}); entries++; sent_bytes[r] += len * a.elem_size;
+                q.push_back(Entry{val, len}); entries++; sent_bytes[r] += len * a.elem_size; pushed[(size_t)r * n + ac.send_peer[i]]++;
                 maxdepth = std::max<int>(maxdepth, (int)q.size());
               }
               progress = true;
@@ -141,7 +159,7 @@ ValidateResult run(const CollArgs& a, int op, bool with_data, int fifo_cap, int6
           }
           if (!advance) break;
           c.act++;
-          if (c.act >= p.actions.size()) { c.act = 0; c.seg++; if (c.seg >= c.maxseg) { c.done = true; progress = true; } }
+          if (c.act >= p.actions.size()) { c.act = 0; c.seg++; if (c.seg >= c.maxseg) { c.done = true; progress = true; if (defer) flush(r); } }
         }
       }
     }
@@ -207,13 +225,13 @@ ValidateResult run(const CollArgs& a, int op, bool with_data, int fifo_cap, int6
 
 }  // namespace
 
-ValidateResult validate(const CollArgs& a, int op, bool integer, int fifo_cap, int64_t seg_elems, int n_cta) {
-  if (integer) return run<int32_t>(a, op, true, fifo_cap, seg_elems, n_cta);
-  return run<float>(a, op, true, fifo_cap, seg_elems, n_cta);
+ValidateResult validate(const CollArgs& a, int op, bool integer, int fifo_cap, int64_t seg_elems, int n_cta, bool defer_publish) {
+  if (integer) return run<int32_t>(a, op, true, fifo_cap, seg_elems, n_cta, defer_publish);
+  return run<float>(a, op, true, fifo_cap, seg_elems, n_cta, defer_publish);
 }
 
-ValidateResult validate_symbolic(const CollArgs& a, int fifo_cap, int n_cta) {
-  return run<float>(a, 0, false, fifo_cap, (int64_t)(256 * 1024) / a.elem_size, n_cta);
+ValidateResult validate_symbolic(const CollArgs& a, int fifo_cap, int n_cta, bool defer_publish) {
+  return run<float>(a, 0, false, fifo_cap, (int64_t)(256 * 1024) / a.elem_size, n_cta, defer_publish);
 }
 
 }  // namespace piccl

@@ -127,11 +127,12 @@ struct ValidateResult {
 // seed 0; int32 in [-1000,1000] when integer=true) with FIFOs of `fifo_cap`
 // entries and segments of `seg_elems` elements, and compares with a serial
 // reduction.  op: 0 sum, 1 prod, 2 max, 3 min.
-ValidateResult validate(const CollArgs& a, int op, bool integer, int fifo_cap, int64_t seg_elems, int n_cta);
+// defer_publish models the executor variant that holds its counter updates back until it is about to block (exec_impl.cuh).
+ValidateResult validate(const CollArgs& a, int op, bool integer, int fifo_cap, int64_t seg_elems, int n_cta, bool defer_publish = false);
 
 // Symbolic check for sizes too large to materialise: coverage of every output
 // element and FIFO order, no data.
-ValidateResult validate_symbolic(const CollArgs& a, int fifo_cap, int n_cta);
+ValidateResult validate_symbolic(const CollArgs& a, int fifo_cap, int n_cta, bool defer_publish = false);
 
 // ---- dumps ----
 // Transfers in the reference's schedule XML format

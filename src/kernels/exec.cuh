@@ -90,6 +90,8 @@ typedef void (*ExecKernelFn)(KernelArgs);
 // [dtype][op 0..3]; filled by the exec_inst_*.cu translation units.
 ExecKernelFn exec_kernel_for(int dtype, int op);
 ExecKernelFn exec_copy_kernel();
+ExecKernelFn exec_defer_kernel_for(int dtype, int op);   // counter updates held back until the CTA is about to block (PICCL_EXEC_DEFER=1)
+ExecKernelFn exec_defer_copy_kernel();
 ExecKernelFn exec_ll_kernel_for(int dtype, int op);   // low-latency variant (exec_ll.cuh)
 ExecKernelFn exec_ll_copy_kernel();
 

@@ -242,7 +242,13 @@ __device__ __noinline__ void reduce_copy_elem(int nsrc, const char* const* src, 
 // ---------------------------------------------------------------- the kernel
 constexpr int kSliceCache = 192;      // actions whose CTA slice is precomputed in shared memory
 
-template <typename T, int OP>
+// DEFER = true (PICCL_EXEC_DEFER=1) postpones the counter updates that end an action: a release store to another GPU waits
+// for the action's data to be acknowledged (a round trip through the switch), and a chain of independent actions, such as the
+// n-1 sends that open a DIRECT all-reduce, pays that once per action.  The deferred variant only bumps its private counters
+// and publishes all of them together, with the fences of the owning threads running side by side, at the first point
+// where the CTA is about to block (one probe of the flags it needs; somebody may be waiting for what was held back) and at
+// the end of the kernel.  Nothing is ever held back across a wait, so progress is as in the plain variant.
+template <typename T, int OP, bool DEFER>
 __global__ void __launch_bounds__(kMaxBlock, 1) exec_kernel(const KernelArgs ka) {
   const int vr = blockIdx.x / ka.n_cta, cta = blockIdx.x % ka.n_cta;
   const LaunchRank& L = ka.r[vr];
@@ -278,6 +284,15 @@ __global__ void __launch_bounds__(kMaxBlock, 1) exec_kernel(const KernelArgs ka)
   char* const my_heap = s_heap[rank];
   WaitCtx w; w.ctx = ctx; w.timeout_ns = ka.timeout_ns; w.cta = cta;
   bool failed = false;
+  // DEFER: what peer `tid` has been told so far, and whether any update is held back (the same value in every thread)
+  unsigned long long pub_sent = my_sent, pub_rcvd = my_rcvd;
+  bool pending = false;
+  auto flush = [&]() {
+    if (tid < nranks) {
+      if (pub_sent != my_sent) { st_release_sys(reinterpret_cast<unsigned long long*>(s_heap[tid] + tail_off + (long long)(rank * max_cta + cta) * kFlagStride), my_sent); pub_sent = my_sent; }
+      if (pub_rcvd != my_rcvd) { st_release_sys(reinterpret_cast<unsigned long long*>(s_heap[tid] + head_off + (long long)(rank * max_cta + cta) * kFlagStride), my_rcvd); pub_rcvd = my_rcvd; }
+    }
+  };
 
   for (int seg = 0; seg < maxseg && !failed; seg++) {
     for (int ai = 0; ai < L.n_actions; ai++) {
@@ -290,6 +305,17 @@ __global__ void __launch_bounds__(kMaxBlock, 1) exec_kernel(const KernelArgs ka)
       const long long len = hi - lo;
       const Action ac = L.actions[ai];
 
+      if (DEFER && pending) {
+        // one probe of everything this action waits for; if anything is missing, tell the peers what was held back first
+        bool block = false;
+        if (tid < nranks) {
+          for (int j = 0; j < ac.n_send; j++) if (ac.send_peer[j] == tid && my_sent + 1 > (unsigned long long)nslot)
+            block |= ld_acquire_sys(reinterpret_cast<const unsigned long long*>(my_heap + head_off + (long long)(tid * max_cta + cta) * kFlagStride)) < my_sent + 1 - nslot;
+          for (int j = 0; j < ac.n_recv; j++) if (ac.recv_peer[j] == tid)
+            block |= ld_acquire_sys(reinterpret_cast<const unsigned long long*>(my_heap + tail_off + (long long)(tid * max_cta + cta) * kFlagStride)) < my_rcvd + 1;
+        }
+        if (__syncthreads_or(block)) { flush(); pending = false; }
+      }
       // ---- wait: credit on every send connection, data on every receive connection
       if (tid < nranks) {
         bool ok = true;
@@ -353,7 +379,13 @@ __global__ void __launch_bounds__(kMaxBlock, 1) exec_kernel(const KernelArgs ka)
       __syncthreads();
 
       // ---- publish: the data to the consumers, the freed slot to the producers
-      if (tid < nranks) {
+      if (DEFER) {
+        if (tid < nranks) {
+          for (int j = 0; j < ac.n_send; j++) if (ac.send_peer[j] == tid) my_sent++;
+          for (int j = 0; j < ac.n_recv; j++) if (ac.recv_peer[j] == tid) my_rcvd++;
+        }
+        pending = true;
+      } else if (tid < nranks) {
         for (int j = 0; j < ac.n_send; j++) if (ac.send_peer[j] == tid) {
           my_sent++;
           st_release_sys(reinterpret_cast<unsigned long long*>(s_heap[tid] + tail_off + (long long)(rank * max_cta + cta) * kFlagStride), my_sent);
@@ -365,6 +397,7 @@ __global__ void __launch_bounds__(kMaxBlock, 1) exec_kernel(const KernelArgs ka)
       }
     }
   }
+  if (DEFER && pending && !failed) flush();
   if (tid < nranks) { ctx->sent[tid * max_cta + cta] = my_sent; ctx->rcvd[tid * max_cta + cta] = my_rcvd; }
 }
 

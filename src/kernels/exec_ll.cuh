@@ -160,6 +160,7 @@ __global__ void __launch_bounds__(kLLBlock) exec_ll_kernel(const KernelArgs ka) 
 
 #define PICCL_INSTANTIATE_EXEC(T, DT)                                                              \
   namespace piccl {                                                                                \
-  ExecKernelFn exec_table_##DT[4] = {exec_kernel<T, 0>, exec_kernel<T, 1>, exec_kernel<T, 2>, exec_kernel<T, 3>}; \
+  ExecKernelFn exec_table_##DT[4] = {exec_kernel<T, 0, false>, exec_kernel<T, 1, false>, exec_kernel<T, 2, false>, exec_kernel<T, 3, false>}; \
+  ExecKernelFn exec_defer_table_##DT[4] = {exec_kernel<T, 0, true>, exec_kernel<T, 1, true>, exec_kernel<T, 2, true>, exec_kernel<T, 3, true>}; \
   ExecKernelFn exec_ll_table_##DT[4] = {exec_ll_kernel<T, 0>, exec_ll_kernel<T, 1>, exec_ll_kernel<T, 2>, exec_ll_kernel<T, 3>}; \
   }

@@ -373,7 +373,10 @@ static int run(piccl_comm** comms, int n, const CallDesc* calls, cudaStream_t st
   const long long count = reducing ? (long long)d0.count : (long long)d0.count * esz_real;
   // small messages of every collective run the low-latency variant of the executor (flags inside the data lines)
   const bool use_llf = c0->llf_max_bytes > 0 && (long long)d0.count * esz_real <= c0->llf_max_bytes;
-  ExecKernelFn fn = use_llf ? (reducing ? exec_ll_kernel_for(d0.dtype, op) : exec_ll_copy_kernel()) : (reducing ? exec_kernel_for(d0.dtype, op) : exec_copy_kernel());
+  const bool defer = env().exec_defer != 0;
+  ExecKernelFn fn = use_llf ? (reducing ? exec_ll_kernel_for(d0.dtype, op) : exec_ll_copy_kernel())
+                   : defer ? (reducing ? exec_defer_kernel_for(d0.dtype, op) : exec_defer_copy_kernel())
+                           : (reducing ? exec_kernel_for(d0.dtype, op) : exec_copy_kernel());
   if (!fn) return fail(PICCL_INTERNAL_ERROR, "no kernel for dtype %d op %d", d0.dtype, op);
 
   // small exchange-type all-reduces take the low-latency kernel (flags travel inside the data lines)

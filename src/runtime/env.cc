@@ -41,6 +41,7 @@ static void load() {
   e.llf_kb = env_int("PICCL_LLF_KB", 64);        // largest message (any collective) on the low-latency executor; 0 turns it off
   e.tp_mb = env_int("PICCL_TP_MB", 0);           // heap space for the fused tensor-parallel kernels (0: none)
   e.tp_feeders = env_int("PICCL_TP_FEEDERS", 24); // CTAs that push the local shard in all-gather -> GEMM
+  e.exec_defer = env_int("PICCL_EXEC_DEFER", 0);
   e.nvls = env_int("PICCL_NVLS", 0);            // 1: build an NVLink multicast window per communicator (algorithm NVLS)
   e.nvls_chunk_kb = env_int("PICCL_NVLS_CHUNK_KB", 256);
   e.nvls_cta = env_int("PICCL_NVLS_CTA", 64);

@@ -1,7 +1,7 @@
 // piccl_sched: command line front end of the schedule layer.
 //   piccl_sched xml      --collective C --algorithm A [--k K] --nodes N --buffer-size BYTES [--root R]
 //   piccl_sched json     ... --rank R
-//   piccl_sched validate ... [--int] [--op sum|prod|max|min] [--in-place] [--cta N] [--fifo N] [--seg ELEMS] [--symbolic]
+//   piccl_sched validate ... [--int] [--op sum|prod|max|min] [--in-place] [--cta N] [--fifo N] [--seg ELEMS] [--symbolic] [--defer]
 // `--buffer-size` is the whole buffer in bytes, as in the reference's generator
 // (tools/schedule_generator/main.py:15-21): for allgather / reduce_scatter each
 // rank contributes buffer_size / nodes.
@@ -32,7 +32,7 @@ int main(int argc, char** argv) {
   if (argc < 2) { fprintf(stderr, "usage: piccl_sched xml|json|validate --collective C --algorithm A [--k K] --nodes N --buffer-size B\n"); return 2; }
   std::string cmd = argv[1];
   // fifo = 2: the smallest FIFO depth the runtime allows (a fused receive + forward needs two entries in flight)
-  CollArgs a; a.elem_size = 4; int rank = 0, op = 0, fifo = 2, cta = 1; bool integer = false, symbolic = false; int64_t seg = 0, bytes = 0;
+  CollArgs a; a.elem_size = 4; int rank = 0, op = 0, fifo = 2, cta = 1; bool integer = false, symbolic = false, defer = false; int64_t seg = 0, bytes = 0;
   for (int i = 2; i < argc; i++) {
     std::string f = argv[i];
     auto val = [&]() -> const char* { if (i + 1 >= argc) { fprintf(stderr, "missing value for %s\n", f.c_str()); exit(2); } return argv[++i]; };
@@ -47,6 +47,7 @@ int main(int argc, char** argv) {
     else if (f == "--int") integer = true;
     else if (f == "--in-place") a.in_place = true;
     else if (f == "--symbolic") symbolic = true;
+    else if (f == "--defer") defer = true;
     else if (f == "--cta") cta = atoi(val());
     else if (f == "--fifo") fifo = atoi(val());
     else if (f == "--seg") seg = atoll(val());
@@ -60,7 +61,7 @@ int main(int argc, char** argv) {
   if (cmd == "json") { puts(dump_json(a, rank).c_str()); return 0; }
   if (cmd == "validate") {
     if (!seg) seg = std::max<int64_t>(4, a.count / 3 / (16 / std::min(16, a.elem_size)) * (16 / std::min(16, a.elem_size)));
-    ValidateResult v = symbolic ? validate_symbolic(a, fifo, cta) : validate(a, op, integer, fifo, seg, cta);
+    ValidateResult v = symbolic ? validate_symbolic(a, fifo, cta, defer) : validate(a, op, integer, fifo, seg, cta, defer);
     printf("%s entries=%lld max_fifo_depth=%d max_abs_err=%g bytes_sent_max_rank=%lld %s\n", v.ok ? "OK" : "FAIL",
            (long long)v.fifo_entries, v.max_fifo_depth, v.max_abs_err, (long long)v.bytes_sent_max_rank, v.error.c_str());
     return v.ok ? 0 : 1;

@@ -21,6 +21,16 @@ def test_all_rank_counts_and_radices(coll, algo):
         assert v.ok, f"{coll} {algo} n={n} k={k} in_place={in_place}: {v.error}"
 
 
+@pytest.mark.parametrize("algo", ALGOS)
+def test_deferred_counter_updates_never_deadlock(algo):
+    """The executor variant that publishes its FIFO counters only when it is about to block (exec_impl.cuh, DEFER):
+    every schedule still terminates with the right data, also with the smallest FIFO."""
+    for coll in COLLS:
+        for n, k, in_place in itertools.product([2, 3, 4, 6, 8, 9, 16], [-1, 2, 4, 8], [False, True]):
+            v = S.validate(coll, algo, n, 257, k=k, root=n - 1, in_place=in_place, n_cta=2, seg_elems=32, fifo_cap=2, deferred=True)
+            assert v.ok, f"{coll} {algo} n={n} k={k} in_place={in_place}: {v.error}"
+
+
 @pytest.mark.parametrize("op", ["sum", "prod", "max", "min"])
 @pytest.mark.parametrize("integer", [False, True])
 def test_ops_exact_for_integers(op, integer):
