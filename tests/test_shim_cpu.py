@@ -140,3 +140,49 @@ def test_fdshare_missing_rank_is_reported_within_the_limit(tmp_path):
     by_rank = {r[0]: r for r in res}
     assert by_rank[0][1] == -1 and "timed out waiting for 1 peer" in by_rank[0][4]
     assert by_rank[1][1] != 0          # rank 1 connected but never got a descriptor
+
+
+# ---------------------------------------------------------------- the interposer in front of a stand-in NCCL, no GPU
+def _fake_nccl_world(tmp_path):
+    native = ROOT / "tests" / "native"
+    lib = tmp_path / "libnccl.so.2"
+    app = tmp_path / "nccl_app"
+    subprocess.run(["gcc", "-shared", "-fPIC", "-Wall", "-Wextra", "-Werror", "-Wl,-soname,libnccl.so.2", str(native / "fake_nccl.c"), "-o", str(lib)], check=True)
+    subprocess.run(["gcc", "-Wall", "-Wextra", "-Werror", str(native / "nccl_app.c"), "-o", str(app), f"-L{tmp_path}", "-l:libnccl.so.2", f"-Wl,-rpath,{tmp_path}"], check=True)
+    return app
+
+
+def _run_app(app, **env):
+    e = dict(os.environ, LD_PRELOAD=str(_so()), PICCL_LOG="1", PICCL_TIMEOUT_MS="2000")
+    e.pop("CUDA_VISIBLE_DEVICES", None)
+    e.update(env)
+    return subprocess.run([str(app)], env=e, capture_output=True, text=True, timeout=120)
+
+
+def test_unset_algorithms_pass_every_call_to_the_real_library(tmp_path):
+    """Reference behaviour: no PICCL_<COLL>_ALGO -> real NCCL (src/piccl.c:53-57 and the like)."""
+    app = _fake_nccl_world(tmp_path)
+    r = _run_app(app)
+    assert r.returncode == 0 and "init=0" in r.stdout and "collectives=0 async=0/0" in r.stdout and "destroy=0" in r.stdout, r.stdout + r.stderr
+    assert "FAKE_NCCL allreduce=2 allgather=2 reduce_scatter=2 reduce=2 broadcast=2 init=1 destroy=1 group=1" in r.stdout
+    assert "allreduce: 0 fused, 2 passed to NCCL" in r.stderr and "broadcast: 0 fused, 2 passed to NCCL" in r.stderr
+
+
+def test_a_communicator_the_executor_cannot_serve_falls_back_without_breaking_the_application(tmp_path):
+    """Algorithms set, but (a) a one-rank communicator, (b) several ranks on a machine where CUDA cannot be initialised:
+    the set-up fails on the host, every call still reaches the real library and returns success."""
+    app = _fake_nccl_world(tmp_path)
+    algos = {f"PICCL_{c}_ALGO": "RING" for c in ("ALLREDUCE", "ALLGATHER", "REDUCE_SCATTER", "REDUCE", "BROADCAST")}
+    r = _run_app(app, **algos)
+    assert r.returncode == 0 and "collectives=0" in r.stdout, r.stdout + r.stderr
+    assert "FAKE_NCCL allreduce=2 allgather=2 reduce_scatter=2 reduce=2 broadcast=2" in r.stdout
+    assert "allreduce: 0 fused, 2 passed to NCCL" in r.stderr
+    import torch
+    if torch.cuda.is_available():
+        assert "communicator with 1 ranks: NCCL is used" in r.stderr
+    else:
+        # no usable CUDA device: the set-up is not even attempted (the stream cannot be queried), with any rank count
+        r = _run_app(app, FAKE_NCCL_RANKS="4", **algos)
+        assert r.returncode == 0 and "collectives=0" in r.stdout, r.stdout + r.stderr
+        assert "FAKE_NCCL allreduce=2 allgather=2 reduce_scatter=2 reduce=2 broadcast=2" in r.stdout
+        assert "allreduce: 0 fused, 2 passed to NCCL" in r.stderr
