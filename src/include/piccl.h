@@ -74,6 +74,10 @@ int piccl_comm_destroy(piccl_comm_t* c);
 int piccl_comm_abort(piccl_comm_t* c);                      /* makes running and future kernels return */
 int piccl_comm_status(piccl_comm_t* c, piccl_status_t* out);/* never blocks */
 int piccl_get_stats(piccl_comm_t* c, piccl_stats_t* out);
+/* What AUTO resolves to for `nranks` ranks: PICCL_TUNE_FILE table first, then the built-in rule; *k gets the radix / group size. */
+int piccl_select_algorithm(int nranks, int coll, unsigned long long bytes, int* k);
+/* The configuration in force as "key=value" pairs; returns the length needed, like snprintf. */
+int piccl_env_describe(char* buf, int len);
 int piccl_comm_rank(piccl_comm_t* c);
 int piccl_comm_nranks(piccl_comm_t* c);
 const char* piccl_last_error(void);                         /* thread-local text of the last failure */

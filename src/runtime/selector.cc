@@ -63,3 +63,13 @@ Algo select_algo_n(int n, Coll coll, size_t bytes, int* k) {
 Algo select_algo(piccl_comm* c, Coll coll, size_t bytes, int* k) { return select_algo_n(c->nranks, coll, bytes, k); }
 
 }  // namespace piccl
+
+// What AUTO resolves to for a communicator of `nranks` ranks (tuning table first, then the built-in rule).
+// Returns the algorithm (PICCL_ALGO_*) and, through *k, the radix or group size (-1 / 2 / n as the rule says).
+extern "C" int piccl_select_algorithm(int nranks, int coll, unsigned long long bytes, int* k) {
+  int kk = -1;
+  if (coll < 0 || coll >= piccl::COLL_COUNT || nranks < 1) return 0;
+  piccl::Algo a = piccl::select_algo_n(nranks, (piccl::Coll)coll, (size_t)bytes, &kk);
+  if (k) *k = kk;
+  return (int)a;
+}

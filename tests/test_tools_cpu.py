@@ -233,3 +233,30 @@ def test_shipped_samples_simulate(tmp_path):
     # the samples are what the generator writes today
     assert (sim / "schedules" / "8_direct_allreduce.xml").read_text() == gen.generate("allreduce", 8, 1 << 24, "direct", 1)
     assert (sim / "schedules" / "8_ring_allgather.xml").read_text() == gen.generate("allgather", 8, 8 * 4097, "ring", 1)
+
+
+def _select_in_child(env_extra, queries):
+    """AUTO's choice for (nranks, collective, bytes) in a fresh process (the tuning table is read once per process)."""
+    code = ("import ctypes as C, sys, json; sys.path.insert(0, %r); from piccl_b200 import _native as N; l = N.lib(); out = []\n"
+            "names = {v: k for k, v in N.ALGO.items()}\n"
+            "for n, coll, b in json.loads(sys.argv[1]):\n"
+            "    k = C.c_int(-9); a = l.piccl_select_algorithm(n, N.COLL[coll], C.c_ulonglong(b), C.byref(k)); out.append([names[a], k.value])\n"
+            "print(json.dumps(out))") % str(ROOT)
+    import json
+    import os
+    r = subprocess.run([sys.executable, "-c", code, json.dumps(queries)], env=dict(os.environ, **env_extra), capture_output=True, text=True, check=True)
+    return json.loads(r.stdout.strip().splitlines()[-1])
+
+
+def test_builtin_rule_and_tuning_table_of_the_library():
+    """src/runtime/selector.cc: the built-in rule, and a table given through PICCL_TUNE_FILE, which wins where it has a row."""
+    q = [[8, "allreduce", 1024], [8, "allreduce", 1 << 20], [8, "allreduce", 1 << 28], [2, "allreduce", 16 << 20], [8, "allgather", 4096],
+         [8, "allgather", 1 << 20], [8, "broadcast", 1 << 20], [4, "reduce_scatter", 8192]]
+    got = _select_in_child({"PICCL_TUNE_FILE": ""}, q)
+    assert got == [["PRM", 8], ["PRD", 2], ["RING", -1], ["RING", -1], ["PRM", 8], ["RING", -1], ["RING", -1], ["PRM", 4]]
+    # the table derived from the 8-GPU sweep: first row of its collective and rank count with max_bytes >= size
+    table = ROOT / "tools" / "selector" / "tables" / "b200_8gpu.csv"
+    got = _select_in_child({"PICCL_TUNE_FILE": str(table)}, [[8, "allreduce", 1024], [8, "allreduce", 32768], [8, "allreduce", 2 << 20], [8, "allreduce", 1 << 30],
+                                                           [4, "allreduce", 1024]])
+    assert got[0] == ["PRM", 8] and got[1] == ["PRM", 2] and got[2] == ["PRM", 2] and got[3][0] == "RING"
+    assert got[4] == ["PRM", 4]                                    # no row for 4 ranks in that table: the built-in rule
