@@ -260,3 +260,31 @@ def test_builtin_rule_and_tuning_table_of_the_library():
                                                            [4, "allreduce", 1024]])
     assert got[0] == ["PRM", 8] and got[1] == ["PRM", 2] and got[2] == ["PRM", 2] and got[3][0] == "RING"
     assert got[4] == ["PRM", 4]                                    # no row for 4 ranks in that table: the built-in rule
+
+
+def test_profile_fitted_from_a_measured_ring_sweep_predicts_the_other_schedules(tmp_path):
+    """tools/loggp_param/fit_from_sweep.py on the committed 8-GPU sweep: the ring is reproduced by construction, the grouped ring within
+    10 %, the recursive all-reduces from 4 MiB within 15 % (median) once the reduction cost per byte is fitted."""
+    import csv
+    import math
+    import re
+    from tools.loggp_param import fit_from_sweep as F
+    from tools.selector import select
+    sweep = str(ROOT / "benchmarks" / "results" / "sweep_8.csv")
+    out = tmp_path / "p.csv"
+    assert F.main([sweep, "--ranks", "8", "--output", str(out)]) == 0
+    rows = [l.split(",") for l in out.read_text().splitlines()[1:]]
+    G = float(rows[0][5])
+    assert 550e9 < 1 / G < 700e9                                   # asymptotic bandwidth per hop, bytes/s: the 600+ GB/s the large ring runs at
+    assert out.read_text() == (ROOT / "tools" / "loggp_sim" / "profiles" / "b200_executor_8gpu_loggp.csv").read_text()
+    gamma, med = F.fit_gamma(sweep, str(out), 8)
+    assert 2e-13 < gamma < 1.2e-12 and med < 0.15
+    meas = {}
+    for r in csv.reader(open(sweep)):
+        m = re.match(r"ours-([A-Z_]+)-k(-?\d+)", r[1]) if len(r) > 8 and r[0] == "allreduce" and r[2] == "float" else None
+        if m and int(r[5]) >= 1024:
+            meas[(m.group(1), int(m.group(2)), int(r[5]))] = float(r[7])
+    for (algo, k, b), t in meas.items():
+        if algo in ("RING", "K_RING"):
+            p = 2.5 + 1e6 * select.predict(str(out), "allreduce", 8, b, algo, k, radix=1, gamma=gamma)
+            assert abs(math.log(p / t)) < (0.01 if algo == "RING" else 0.10), (algo, k, b, p, t)
