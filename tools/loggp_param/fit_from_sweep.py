@@ -53,8 +53,10 @@ def write_profile(rows, out: str) -> None:
 
 
 def fit_gamma(path: str, profile: str, ranks: int, dtype: str = "float", launch_us: float = 2.5, min_bytes: int = 4 << 20):
-    """Reduction cost per received byte that best explains the measured recursive all-reduces (PRD / PRM rows of the sweep),
-    given the profile fitted from the ring.  Grid search on the squared log ratio; returns (gamma, median |log ratio|)."""
+    """Cost per received byte that best explains the measured recursive all-reduces (PRD / PRM rows of the sweep), given the
+    profile fitted from the ring: those schedules send in one pass and receive-and-reduce in another, a ring hop does both
+    at once (and that is inside the fitted message cost), so the term applies to them only (tools/selector/select.py: predict).
+    Grid search on the squared log ratio; returns (gamma, median |log ratio|)."""
     import math
     import re
     from pathlib import Path

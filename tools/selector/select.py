@@ -45,7 +45,10 @@ def predict(profile: str, coll: str, n: int, nbytes: int, algo: str, k: int, rad
         sched = Path(d) / "s.xml"
         total = nbytes * n if coll in ("allgather", "reduce_scatter") else nbytes
         sched.write_text(gen.generate("bcast" if coll == "broadcast" else coll, n, max(total, n), algo, max(k, 1)))
-        return S.simulate(sched, topo, radix=radix, gamma=gamma if coll in ("allreduce", "reduce", "reduce_scatter") else 0.0)
+        # gamma: cost per received byte of the separate receive-and-reduce pass of the recursive and direct schedules; a ring hop
+        # reduces while it forwards, and that is already part of a message cost fitted from a ring (fit_from_sweep.py)
+        reducing = coll in ("allreduce", "reduce", "reduce_scatter") and algo not in ("RING", "K_RING")
+        return S.simulate(sched, topo, radix=radix, gamma=gamma if reducing else 0.0)
 
 
 def compress(rows):
