@@ -1,9 +1,10 @@
 #!/bin/bash
 # Collective sweeps for the baseline table: this library, stock NCCL and the reference build, same harness
 # (coll_bench), only LD_PRELOAD and the PICCL_* variables change.
-#   benchmarks/run_sweeps.sh N OUTDIR [quick|lean]
+#   benchmarks/run_sweeps.sh N OUTDIR [quick|lean|focus]
 # quick: fewer iterations and smaller maxima; lean: additionally every second size and a reduced set of variants
-# (what fits a few minutes on 8 GPUs).
+# (what fits a few minutes on 8 GPUs); focus: all-reduce only, the candidates for mid-size and large messages (ring, recursive doubling,
+# DIRECT with and without lazy counter updates, in-switch reduction plain and pipelined) against NCCL.
 # Writes OUTDIR/sweep_<N>.csv (all rows) .  Reference rows are only produced for configurations in which the
 # reference is valid (fp32/int32, allreduce all algorithms, allgather RING/K_RING/PRD/PRM with k a power that
 # fits, reduce RING, broadcast RING/K_RING in place); its stubs and unsafe configurations are not run.
@@ -16,9 +17,25 @@ STEP=2; AR_MIN=8; LEAN=""; [ "$QUICK" = "lean" ] && { STEP=4; AR_MIN=16; LEAN=1;
 run() {  # label preload coll algo k dtype min max extra...
   local label=$1 pre=$2 coll=$3 algo=$4 k=$5 dt=$6 min=$7 max=$8; shift 8
   local up; up=$(echo "$coll" | tr a-z A-Z)
-  env ${pre:+LD_PRELOAD=$pre} ${algo:+PICCL_${up}_ALGO=$algo} ${k:+PICCL_${up}_K=$k} timeout 300 $CB --gpus $N --coll $coll --dtype $dt --min $min --max $max \
+  local extra_env=(); while [ $# -gt 0 ] && [[ "$1" == [A-Z]*=* ]]; do extra_env+=("$1"); shift; done   # leading VAR=VALUE words: environment
+  env "${extra_env[@]}" ${pre:+LD_PRELOAD=$pre} ${algo:+PICCL_${up}_ALGO=$algo} ${k:+PICCL_${up}_K=$k} timeout 300 $CB --gpus $N --coll $coll --dtype $dt --min $min --max $max \
       --check --label "$label" --iters-small $IS --iters-large $IL --step $STEP "$@" 2>/dev/null | grep -v "^#\|^\[PICCL\|NCCL version\|PICCL_" >> "$CSV"
 }
+if [ "$QUICK" = "focus" ]; then
+  IS=200; IL=20; STEP=4
+  for dt in float bf16; do
+    run nccl "" allreduce "" "" $dt 65536 1073741824
+    run nccl-nvls-off "" allreduce "" "" $dt 65536 1073741824 NCCL_NVLS_ENABLE=0
+    run ours-RING-k-1 $OURS allreduce RING "" $dt 65536 1073741824
+    run ours-PRD-k-1 $OURS allreduce PRD "" $dt 65536 1073741824
+    run ours-DIRECT-k-1 $OURS allreduce DIRECT "" $dt 65536 1073741824
+    run oursdefer-DIRECT-k-1 $OURS allreduce DIRECT "" $dt 65536 1073741824 PICCL_EXEC_DEFER=1     # lazy counter updates
+    run ours-NVLS-k-1 $OURS allreduce NVLS "" $dt 65536 1073741824 PICCL_NVLS=1
+    run ourspipe-NVLS-k-1 $OURS allreduce NVLS "" $dt 65536 1073741824 PICCL_NVLS=1 PICCL_NVLS_PIPE=1   # pipelined kernel
+    run ourspipe128-NVLS-k-1 $OURS allreduce NVLS "" $dt 65536 1073741824 PICCL_NVLS=1 PICCL_NVLS_PIPE=1 PICCL_NVLS_CTA=128
+  done
+  echo "rows: $(wc -l < "$CSV")"; exit 0
+fi
 KS="2 4"; [ "$N" -ge 8 ] && KS="2 4 8"
 AR_MAX=1073741824; BLK_MAX=268435456; [ "$QUICK" = "quick" ] && { AR_MAX=268435456; BLK_MAX=67108864; }
 if [ -n "$LEAN" ]; then
