@@ -98,6 +98,15 @@ def ops_lib() -> C.CDLL:
         return _libs["ops"]
 
 
+def gemm2_lib() -> C.CDLL:
+    """The CTA-pair GEMM (libpiccl_gemm2.so); raises if the library or its source is not present."""
+    with _lock:
+        if "gemm2" not in _libs:
+            path = _ensure_built("libpiccl_gemm2.so")
+            _libs["gemm2"] = C.CDLL(str(path), mode=C.RTLD_LOCAL)
+        return _libs["gemm2"]
+
+
 def last_error() -> str:
     return (lib().piccl_last_error() or b"").decode()
 

@@ -41,3 +41,22 @@ def gemm_nt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None, gelu
         raise RuntimeError(f"piccl_ops_gemm_bf16_nt failed (code {rc}) for M={M} N={Nn} K={K}")
     _bump()
     return out
+
+
+def gemm_nt_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias=None) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T + bias on CTA pairs (`tcgen05.mma.cta_group::2`, src/ops2/gemm_sm100_2cta.cu).
+    M and N multiples of 256, K a multiple of 64.  Opt-in: nothing in the package calls it by default."""
+    M, K = x.shape
+    Nn = w.shape[0]
+    rc = N.gemm2_lib().piccl_ops2_gemm_bf16_nt(C.c_void_p(x.data_ptr()), C.c_void_p(w.data_ptr()), C.c_void_p(out.data_ptr()),
+                                               C.c_void_p(bias.data_ptr() if bias is not None else 0), M, Nn, K,
+                                               C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    if rc != 0:
+        raise RuntimeError(f"piccl_ops2_gemm_bf16_nt failed (code {rc}) for M={M} N={Nn} K={K}")
+    _bump()
+    return out
+
+
+def pair_status() -> int:
+    """0, or the role whose bounded wait ran out in the CTA-pair GEMM since the last call (synchronises the device)."""
+    return int(N.gemm2_lib().piccl_ops2_gemm_status())
