@@ -288,3 +288,21 @@ def test_profile_fitted_from_a_measured_ring_sweep_predicts_the_other_schedules(
         if algo in ("RING", "K_RING"):
             p = 2.5 + 1e6 * select.predict(str(out), "allreduce", 8, b, algo, k, radix=1, gamma=gamma)
             assert abs(math.log(p / t)) < (0.05 if algo == "RING" else 0.10), (algo, k, b, p, t)      # the ring was fitted without the reduction cost
+
+
+def test_trace_summary(tmp_path, capsys):
+    """tools/trace/summarize.py on files in the format src/runtime/trace.cu writes."""
+    import json
+    from tools.trace import summarize as T
+    for rank in range(2):
+        ev = [{"name": "allreduce/RING", "ph": "X", "pid": rank, "tid": 0, "ts": 10.0 * i, "dur": 100.0 + rank, "args": {"bytes": 26214400, "k": 0, "ctas": 64}} for i in range(3)]
+        ev.append({"name": "allgather/PRM", "ph": "X", "pid": rank, "tid": 0, "ts": 99.0, "dur": 8.0, "args": {"bytes": 4096, "k": 8, "ctas": 1}})
+        (tmp_path / f"run.{rank}.json").write_text(json.dumps({"traceEvents": ev}))
+    files, events = T.load([str(tmp_path / "run")])
+    assert len(files) == 2 and len(events) == 8
+    rows, per_rank = T.summarize(events)
+    assert rows[0]["collective"] == "allreduce" and rows[0]["algorithm"] == "RING" and rows[0]["size"] == "<=64M" and rows[0]["calls"] == 6
+    assert abs(rows[0]["algbw_GBs"] - 26214400 / 100.5 / 1e3) < 0.5
+    assert rows[1]["size"] == "<=4K" and per_rank[1] > per_rank[0]
+    assert T.main([str(tmp_path / "run.0.json")]) == 0 and "4 calls in 1 file" in capsys.readouterr().out
+    assert T.bucket(1 << 31) == ">1G" and T.bucket(1024) == "<=1K" and T.bucket(1025) == "<=4K"
