@@ -45,6 +45,7 @@ static void load() {
   e.nvls = env_int("PICCL_NVLS", 0);            // 1: build an NVLink multicast window per communicator (algorithm NVLS)
   e.nvls_chunk_kb = env_int("PICCL_NVLS_CHUNK_KB", 256);
   e.nvls_cta = env_int("PICCL_NVLS_CTA", 64);
+  { const char* g = getenv("PICCL_NVLS_GRAN"); e.nvls_gran_min = g && !strcmp(g, "min"); }
   e.nvls_pipe = env_int("PICCL_NVLS_PIPE", 0);   // 1: the pipelined kernel (two half slots per CTA)
   // PICCL_PROTO narrows the choice of data path that is otherwise made per call by message size:
   //   auto    (default) low-latency kernels for small messages, the FIFO executor otherwise

@@ -153,8 +153,10 @@ void nvls_setup(piccl_comm* c, int root_pid, unsigned long long root_id) {
   ap.type = CU_MEM_ALLOCATION_TYPE_PINNED; ap.location.type = CU_MEM_LOCATION_TYPE_DEVICE; ap.location.id = c->device;
   ap.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
   size_t g_mc = 0, g_mem = 0;
-  STEP(d.MulticastGetGranularity(&g_mc, &mp, CU_MULTICAST_GRANULARITY_RECOMMENDED));
-  STEP(d.MemGetAllocationGranularity(&g_mem, &ap, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED));
+  // PICCL_NVLS_GRAN=min: the smallest granularity the driver accepts instead of the recommended one (512 MiB per window on B200)
+  const bool gran_min = e.nvls_gran_min != 0;
+  STEP(d.MulticastGetGranularity(&g_mc, &mp, gran_min ? CU_MULTICAST_GRANULARITY_MINIMUM : CU_MULTICAST_GRANULARITY_RECOMMENDED));
+  STEP(d.MemGetAllocationGranularity(&g_mem, &ap, gran_min ? CU_MEM_ALLOC_GRANULARITY_MINIMUM : CU_MEM_ALLOC_GRANULARITY_RECOMMENDED));
   size_t gran = std::max<size_t>(std::max(g_mc, g_mem), 4096);
   s->win = (want + gran - 1) / gran * gran;
   mp.size = s->win;
