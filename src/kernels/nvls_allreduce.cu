@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(kNvlsBlock, 2) nvls_allreduce_pipe_kernel(cons
   __syncthreads();
   const long long nchunks = (a.bytes + a.chunk_bytes - 1) / a.chunk_bytes;
   const long long m = cta < nchunks ? (nchunks - cta + a.n_cta - 1) / a.n_cta : 0;          // chunks of this CTA
-  const long long half = a.slot_bytes / 2;
+  const long long half = (a.slot_bytes / 2) / 16 * 16;        // second half slot, 16-byte aligned for any rank count
   char* const my0 = a.uc + kNvlsFlagBytes + (long long)cta * a.slot_bytes;
   char* const mc0 = a.mc + kNvlsFlagBytes + (long long)cta * a.slot_bytes;
   // counters of this CTA index: A0, A1, B0, B1
