@@ -1,6 +1,6 @@
 """Property tests of the LogGP simulator (tools/loggp_sim/sim.py): random acyclic schedules on a two-level topology always
 finish (in the classical and in the reference-compatible accounting), never faster than their longest dependency chain allows,
-never faster when a message grows or when ports are taken away.  Malformed inputs are refused with
+deterministically; a single chain of dependent transfers costs exactly the sum of its uncontended message costs.  Malformed inputs are refused with
 a message instead of a traceback from deep inside."""
 import random
 import sys
@@ -60,14 +60,13 @@ def test_random_schedules_finish_and_respect_the_model(tmp_path, seed, n, radix)
     for i, (sz, a, b, deps) in enumerate(tr):
         best[i] = max([best[d] for d in deps], default=0.0) + 5 + (sz - 1) * 1 + 10 + 6
     assert t_clean >= max(best) - 1e-6
-    # a larger message never makes the schedule faster; fewer ports never make it faster
-    j = seed % n
-    bigger = list(tr); bigger[j] = (tr[j][0] * 2 + 7, *tr[j][1:])
-    assert S.simulate(_write(tmp_path, bigger, "b.xml"), topo, radix=radix) >= t_clean - 1e-9
-    if radix > 1:
-        assert S.simulate(_write(tmp_path, tr), topo, radix=1) >= t_clean - 1e-9
-    # a reduction cost and a fixed cost per transfer only add time
-    assert S.simulate(_write(tmp_path, tr), topo, radix=radix, gamma=0.5, alpha=3.0) >= t_clean + 3.0 - 1e-9
+    # (no monotonicity claims: with first-come-first-served ports a longer message or a missing port can reorder the contention
+    # and shorten the schedule, the classic list-scheduling anomaly)
+    assert S.simulate(_write(tmp_path, tr, "again.xml"), topo, radix=radix) == t_clean            # deterministic
+    # without contention (every transfer on its own pair of nodes is impossible here, so: a single chain) the bound is met exactly
+    chain = [(sz, i % 4, (i + 1) % 4, [i - 1] if i else []) for i, (sz, _, _, _) in enumerate(tr)]
+    exact = sum(5 + (sz - 1) * 1 + 10 + 6 for sz, _, _, _ in chain)
+    assert S.simulate(_write(tmp_path, chain, "chain.xml"), topo, radix=radix) == pytest.approx(exact)
 
 
 def test_malformed_inputs_are_refused(tmp_path):

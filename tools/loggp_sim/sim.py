@@ -149,12 +149,14 @@ class Ports:
     def __init__(self, count):
         self.free = [0.0] * count          # busy until
         self.mark = [-1e300] * count       # reference point of the gap rule (start or end of the last use)
+        self.after = [0.0] * count         # classical model: the gap the LAST use of the port imposes, max(g, G s) of that message
 
-    def reserve(self, t: float, gap: float):
-        """earliest (time, port) at which a use may start for a request made at t"""
+    def reserve(self, t: float, gap):
+        """earliest (time, port) at which a use may start for a request made at t.
+        gap: spacing from the port's mark; None = the spacing recorded by the port's previous use (`after`)"""
         best, bi = None, 0
         for i in range(len(self.free)):
-            s = max(t, self.free[i], self.mark[i] + gap)
+            s = max(t, self.free[i], self.mark[i] + (self.after[i] if gap is None else gap))
             if best is None or s < best:
                 best, bi = s, i
         return best, bi
@@ -209,8 +211,9 @@ class Simulator:
                 task.start = now
                 post(now + self.alpha + p("o_s", s), 1, task)
             elif stage == 1:                                 # inject: send port (+ source NIC)
-                gap = g if self.compat else max(g, G * s)
-                st, pi = self.send[task.src].reserve(now, gap)
+                # reference-compatible: g of this message after the end of the last use; classical: the gap belongs to the
+                # message that used the port before (a short message does not make the next, longer one wait for its own length)
+                st, pi = self.send[task.src].reserve(now, g if self.compat else None)
                 nic = self.nic_s.get(self.topo.group0[task.src]) if inter else None
                 if nic is not None:
                     ns, ni = nic.reserve(st, 0.0)
@@ -221,11 +224,18 @@ class Simulator:
                 ports = self.send[task.src]
                 ports.free[pi] = st + wire
                 ports.mark[pi] = st + wire if self.compat else st
+                ports.after[pi] = max(g, G * s)
                 arrive_state[tid] = st
                 post(st + wire + p("L", s), 2, task)
             elif stage == 2:                                 # arrival: destination NIC, receive port
-                gap = g if self.compat else max(g, G * s)
-                st, pi = self.recv[task.dst].reserve(now, gap)
+                if self.compat:
+                    st, pi = self.recv[task.dst].reserve(now, g)
+                else:
+                    # classical: `now` is when the last byte would arrive on an idle port.  A port takes the bytes of one message
+                    # at a time, so if another message was still arriving, this one ends max(g, G s) after that one ended.
+                    rp = self.recv[task.dst]
+                    pi = min(range(len(rp.free)), key=lambda i: rp.free[i])
+                    st = max(now, rp.free[pi] + max(g, G * s)) if rp.free[pi] > 0.0 else now
                 nic = self.nic_r.get(self.topo.group0[task.dst]) if inter else None
                 if nic is not None:
                     ns, ni = nic.reserve(st, 0.0)
