@@ -306,3 +306,34 @@ def test_trace_summary(tmp_path, capsys):
     assert rows[1]["size"] == "<=4K" and per_rank[1] > per_rank[0]
     assert T.main([str(tmp_path / "run.0.json")]) == 0 and "4 calls in 1 file" in capsys.readouterr().out
     assert T.bucket(1 << 31) == ">1G" and T.bucket(1024) == "<=1K" and T.bucket(1025) == "<=4K"
+
+
+def test_fitter_recovers_random_parameters_and_refuses_degenerate_input(tmp_path):
+    """Synthetic PRTT data from known LogGP parameters (with the formulas of the docstring inverted) come back within rounding,
+    for random parameter sets; a train of a single message cannot be fitted and says so."""
+    rng = np.random.default_rng(7)
+    for trial in range(20):
+        L, g, G = rng.uniform(1e-6, 2e-5), rng.uniform(1e-7, 5e-6), rng.uniform(1e-12, 1e-10)
+        n, d = int(rng.integers(2, 40)), rng.uniform(0, 1e-5)
+        sizes = np.unique(rng.integers(1, 1 << 22, size=8))
+        rows = []
+        for s in sizes:
+            o_s, o_r = rng.uniform(1e-7, 5e-6), rng.uniform(1e-7, 5e-6)
+            p1 = 2 * L if s == sizes[0] else rng.uniform(1e-6, 1e-4)
+            pn0 = p1 + (n - 1) * (g + G * (s - 1))
+            pnd = p1 + (n - 1) * (o_s + d)
+            psrv = (n - 1) * (o_r + d)
+            rows.append((s, n, d, p1, pn0, pnd, psrv, o_s, o_r))
+        raw = tmp_path / f"raw{trial}.txt"
+        raw.write_text("size n d p1 pn0 pnd psrv\n" + "\n".join(" ".join(repr(float(x)) for x in r[:7]) for r in rows) + "\n")
+        t = fitter.fit(fitter.read_raw(raw))
+        assert t[0, 1] == pytest.approx(L, rel=1e-9) and t[0, 4] == pytest.approx(g, rel=1e-4, abs=1e-12) and t[0, 5] == pytest.approx(G, rel=1e-6)
+        for row, r in zip(t, rows):
+            assert row[2] == pytest.approx(r[7], rel=1e-6, abs=1e-12) and row[3] == pytest.approx(r[8], rel=1e-6, abs=1e-12)
+    bad = tmp_path / "bad.txt"
+    bad.write_text("64 1 0 1e-5 1e-5 1e-5 1e-5\n128 1 0 1e-5 1e-5 1e-5 1e-5\n")
+    with pytest.raises(ValueError, match="n >= 2"):
+        fitter.fit(fitter.read_raw(bad))
+    with pytest.raises(ValueError, match="no data rows"):
+        (tmp_path / "empty.txt").write_text("only a header\n")
+        fitter.read_raw(tmp_path / "empty.txt")

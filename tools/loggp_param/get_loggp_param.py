@@ -40,6 +40,8 @@ def read_raw(path) -> np.ndarray:
 
 def fit(raw: np.ndarray) -> np.ndarray:
     size, n, d, p1, pn0, pnd, psrv = raw.T
+    if np.any(n < 2):
+        raise ValueError("PRTT rows need n >= 2 messages per train (the gap is (PRTT(n,0,s) - PRTT(1,0,s)) / (n - 1))")
     gap = (pn0 - p1) / (n - 1)
     if len(size) >= 2 and np.ptp(size) > 0:
         G, g = np.polyfit(size - 1, gap, 1)
