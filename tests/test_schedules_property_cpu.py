@@ -13,7 +13,7 @@ from piccl_b200 import schedule as S  # noqa: E402
 
 COLLS = ["allgather", "allreduce", "broadcast", "reduce", "reduce_scatter"]
 ALGOS = ["RING", "K_RING", "RD", "RM", "PRD", "PRM", "DIRECT"]
-COMMON = dict(deadline=None, derandomize=True, suppress_health_check=[HealthCheck.too_slow])
+COMMON = dict(deadline=None, derandomize=True, database=None, suppress_health_check=[HealthCheck.too_slow])
 
 
 @settings(max_examples=400, **COMMON)
