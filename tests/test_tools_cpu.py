@@ -337,3 +337,13 @@ def test_fitter_recovers_random_parameters_and_refuses_degenerate_input(tmp_path
     with pytest.raises(ValueError, match="no data rows"):
         (tmp_path / "empty.txt").write_text("only a header\n")
         fitter.read_raw(tmp_path / "empty.txt")
+
+
+def test_cpu_only_schedule_check_script(tmp_path):
+    """benchmarks/config1_cpu.py: validator + generator + simulator over the headline sizes (data up to 1 MiB here to stay quick)."""
+    out = tmp_path / "c1.csv"
+    r = subprocess.run([sys.executable, str(ROOT / "benchmarks" / "config1_cpu.py"), "--out", str(out), "--data-max", str(1 << 20)], capture_output=True, text=True)
+    assert r.returncode == 0 and "0 failed" in r.stdout, r.stdout + r.stderr
+    rows = [l.split(",") for l in out.read_text().splitlines()[1:]]
+    assert len(rows) == 28 * 7 and all(x[4] == "ok" for x in rows)
+    assert {x[3] for x in rows if int(x[2]) <= 1 << 20} == {"data"} and {x[3] for x in rows if int(x[2]) > 1 << 20} == {"symbolic"}
