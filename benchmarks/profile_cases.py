@@ -3,6 +3,8 @@
     python benchmarks/profile_cases.py exec      # fused collective executor: 2 virtual ranks, ring all-reduce of 256 MiB fp32
     python benchmarks/profile_cases.py exec_ll   # low-latency all-reduce, 8 virtual ranks, 16 KiB
     python benchmarks/profile_cases.py gemm      # tcgen05 GEMM 8192 x 8192 x 3584 bf16
+    python benchmarks/profile_cases.py gemm_pair # the same product on CTA pairs (tcgen05.mma.cta_group::2); checks the result first
+    python benchmarks/profile_cases.py direct    # DIRECT all-reduce, 8 virtual ranks, 16 MiB fp32 (add PICCL_EXEC_DEFER=1 for lazy counters)
     python benchmarks/profile_cases.py tp        # fused GEMM -> reduce-scatter, 2 virtual ranks, 4096 x 4096 x 2048
     python benchmarks/profile_cases.py ln        # residual-add + LayerNorm forward/backward, 8192 x 1024
     python benchmarks/profile_cases.py ce        # cross entropy forward+backward, 8192 x 50304
@@ -42,6 +44,35 @@ def case_gemm():
     for _ in range(4):
         gemm_sm100.gemm_nt(a, b, o)
     torch.cuda.synchronize()
+
+
+def case_gemm_pair():
+    from piccl_b200.ops import gemm_sm100
+    a = torch.randn(8192, 3584, device="cuda").to(torch.bfloat16)
+    b = (torch.randn(8192, 3584, device="cuda") * 0.05).to(torch.bfloat16)
+    o = torch.empty(8192, 8192, device="cuda", dtype=torch.bfloat16)
+    gemm_sm100.gemm_nt_pair(a, b, o)
+    st = gemm_sm100.pair_status()
+    assert st == 0, f"a bounded wait ran out (role {st})"
+    ref = torch.mm(a, b.t())
+    err = (o.float() - ref.float()).abs().max().item()
+    assert err < 0.05 * ref.float().abs().max().item(), err
+    for _ in range(3):
+        gemm_sm100.gemm_nt_pair(a, b, o)
+    torch.cuda.synchronize()
+
+
+def case_direct():
+    from piccl_b200.parallel.comm import LoopbackGroup
+    n, count = 8, 4 << 20
+    g = LoopbackGroup(n)
+    xs = [torch.full((count,), float(r + 1), device="cuda") for r in range(n)]
+    outs = [torch.empty_like(x) for x in xs]
+    for _ in range(4):
+        g.run("allreduce", xs, outs, count, algo="DIRECT")
+    torch.cuda.synchronize()
+    assert g.status().aborted == 0 and float(outs[3][12345]) == n * (n + 1) / 2
+    g.close()
 
 
 def case_tp():
@@ -85,5 +116,5 @@ def case_ce():
 
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "exec"
-    {"exec": case_exec, "exec_ll": lambda: case_exec(True), "gemm": case_gemm, "tp": case_tp, "ln": case_ln, "ce": case_ce}[which]()
+    {"exec": case_exec, "exec_ll": lambda: case_exec(True), "gemm": case_gemm, "gemm_pair": case_gemm_pair, "direct": case_direct, "tp": case_tp, "ln": case_ln, "ce": case_ce}[which]()
     print(f"profile case {which} done")
