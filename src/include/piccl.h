@@ -36,7 +36,7 @@ typedef struct {
   long long slot_bytes;   /* bytes per FIFO slot; 0: PICCL_SLOT_KB or 512 KiB */
   long long scratch_bytes;/* local scratch for recursive reduce-scatter; 0: default 64 MiB */
   int block_size;         /* threads per CTA; 0: PICCL_BLOCK_SIZE or 512 */
-  int timeout_ms;         /* bound of every device-side wait; 0: PICCL_TIMEOUT_MS or 120000 */
+  int timeout_ms;         /* bound of every device-side wait; 0: PICCL_TIMEOUT_MS or 10000 */
   long long tp_bytes;     /* workspace of the fused tensor-parallel kernels; 0: PICCL_TP_MB (default none) */
 } piccl_config_t;
 

@@ -2,6 +2,7 @@
 // Same two-pass scheme as piccl_ops_colsum in elementwise.cu — per-block partial
 // sums in fp32, then one pass that folds the partials — but the partials live in
 // a fixed device array that is part of the library image.
+#include <cstdint>
 #include <cstdio>
 #include <mutex>
 #include "colsum_noalloc.h"
@@ -67,6 +68,8 @@ extern "C" int piccl_ops_colsum_noalloc(const void* x, void* out, int rows, int 
     return -2;
   }
   if (rows < 1) { fprintf(stderr, "piccl_ops_colsum_noalloc: rows = %d must be at least 1\n", rows); return -3; }
+  // x is read as 16-byte vectors (8 bf16 at a time); out is accessed element by element and needs no more than its natural alignment
+  if (reinterpret_cast<uintptr_t>(x) & 15) { fprintf(stderr, "piccl_ops_colsum_noalloc: x = %p is not 16-byte aligned\n", x); return -7; }
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { fprintf(stderr, "piccl_ops_colsum_noalloc: no usable current device\n"); return -5; }
   float* scratch;

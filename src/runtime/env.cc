@@ -32,7 +32,7 @@ static void load() {
   e.block_size = env_int("PICCL_BLOCK_SIZE", 1024, &e.block_size_set);
   e.max_grid = env_int("PICCL_MAX_GRID_SIZE", 1024, &e.max_grid_set);
   e.min_grid = env_int("PICCL_MIN_GRID_SIZE", 1, &e.min_grid_set);
-  e.timeout_ms = env_int("PICCL_TIMEOUT_MS", 120000);
+  e.timeout_ms = env_int("PICCL_TIMEOUT_MS", 10000);
   e.scratch_mb = env_int("PICCL_SCRATCH_MB", 64);
   e.slot_kb = env_int("PICCL_SLOT_KB", 512);
   e.nslot = env_int("PICCL_NSLOT", 4);

@@ -33,7 +33,7 @@ def test_matches_regular_entry_point_on_two_calls_in_a_row():
     stream = torch.cuda.current_stream().cuda_stream
     g = torch.Generator(device="cuda").manual_seed(0)
     # two different shapes back to back: the second call reuses the workspace the first one left dirty
-    shapes = [(8192, 4096), (1000, 1024)]
+    shapes = [(8192, 4096), (1000, 1024), (300, 16384)]            # the last one is as wide as the built-in workspace allows
     xs = [(torch.randn(r, c, generator=g, device="cuda")).to(torch.bfloat16) for r, c in shapes]
     outs = [torch.full((c,), float("nan"), device="cuda", dtype=torch.bfloat16) for _, c in shapes]
     for x, o in zip(xs, outs):
@@ -61,4 +61,5 @@ def test_rejects_what_does_not_fit(capfd):
     assert fn(x.data_ptr(), o.data_ptr(), 8, 12, 0, 0) == -1
     assert fn(x.data_ptr(), o.data_ptr(), 0, 8, 0, 0) == -3
     assert fn(0, o.data_ptr(), 8, 8, 0, 0) == -4
+    assert fn(x.data_ptr() + 2, o.data_ptr(), 7, 8, 0, 0) == -7         # a view that starts one element into the buffer
     assert "exceeds the built-in workspace" in capfd.readouterr().err
