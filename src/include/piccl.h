@@ -24,7 +24,7 @@ enum { PICCL_ALLGATHER = 0, PICCL_ALLREDUCE = 1, PICCL_BROADCAST = 2, PICCL_REDU
 enum { PICCL_ALGO_DEFAULT = 0, PICCL_ALGO_RING = 1, PICCL_ALGO_K_RING = 2, PICCL_ALGO_RD = 3, PICCL_ALGO_RM = 4,
        PICCL_ALGO_PRD = 5, PICCL_ALGO_PRM = 6, PICCL_ALGO_AUTO = 7,
        PICCL_ALGO_DIRECT = 8 /* every rank exchanges with every other rank at once; at most 8 ranks */,
-       PICCL_ALGO_NVLS = 9 /* all-reduce summed inside the NVSwitch; needs PICCL_NVLS=1, else runs RING */ };
+       PICCL_ALGO_NVLS = 9 /* through the NVSwitch: multimem load-reduce / multicast stores; without a multicast window the peer-to-peer choice of AUTO runs */ };
 /* result codes: 0 ok; others mirror ncclResult_t */
 enum { PICCL_OK = 0, PICCL_CUDA_ERROR = 1, PICCL_SYSTEM_ERROR = 2, PICCL_INTERNAL_ERROR = 3, PICCL_INVALID_ARGUMENT = 4,
        PICCL_INVALID_USAGE = 5, PICCL_REMOTE_ERROR = 6, PICCL_UNSUPPORTED = 100 };
@@ -48,7 +48,7 @@ typedef struct { unsigned char bytes[128]; } piccl_handle_t;
 typedef struct {
   int aborted;      /* 1 after a device-side wait ran out or piccl_comm_abort() */
   int code;         /* 1: wait for FIFO credit, 2: wait for FIFO data, 3: aborted by host/peer CTA,
-                       5 / 6: in-switch all-reduce, barrier before / after the reduction (segment = chunk) */
+                       5 / 6 / 7: in-switch collective, wait for a chunk to be filled / reduced / consumed by all ranks (segment = chunk) */
   int rank, cta, action, peer, segment;
   unsigned long long want, have;   /* counter value waited for / last seen */
 } piccl_status_t;
@@ -61,7 +61,7 @@ typedef struct {
   unsigned long long fallbacks;     /* calls the executor declined (reason logged with PICCL_LOG>=1) */
   unsigned long long timeouts;
   unsigned long long persistent_calls; /* calls served by the persistent launcher instead of a kernel launch */
-  unsigned long long nvls_calls;       /* all-reduces summed inside the switch */
+  unsigned long long nvls_calls;       /* collectives run through the switch */
 } piccl_stats_t;
 
 /* ---- communicator life cycle ----
@@ -76,6 +76,8 @@ int piccl_comm_status(piccl_comm_t* c, piccl_status_t* out);/* never blocks */
 int piccl_get_stats(piccl_comm_t* c, piccl_stats_t* out);
 /* What AUTO resolves to for `nranks` ranks: PICCL_TUNE_FILE table first, then the built-in rule; *k gets the radix / group size. */
 int piccl_select_algorithm(int nranks, int coll, unsigned long long bytes, int* k);
+/* The same for a communicator that has (have_window != 0) or lacks an NVLink multicast window. */
+int piccl_select_algorithm_ex(int nranks, int coll, unsigned long long bytes, int have_window, int* k);
 /* The configuration in force as "key=value" pairs; returns the length needed, like snprintf. */
 int piccl_env_describe(char* buf, int len);
 int piccl_comm_rank(piccl_comm_t* c);

@@ -1,55 +1,75 @@
-// All-reduce through the NVSwitch: contributions are summed inside the switch
-// (`multimem.ld_reduce`) and the sum is written to every GPU at once
-// (`multimem.st`), so each GPU sends and receives the vector about once instead
-// of 2(n-1)/n times.  The reference has no counterpart (its all-reduce is a
-// sequence of ncclSend/ncclRecv groups and separate reduce kernels,
-// src/coll/allreduce.c:97-614).
+// Collectives through the NVSwitch: contributions are summed inside the switch
+// (`multimem.ld_reduce`) and results are written to every GPU at once
+// (`multimem.st`), so a GPU sends and receives each byte about once instead of
+// (n-1) times.  All five collectives take this path for large messages.  The
+// reference has no counterpart: its collectives are sequences of
+// ncclSend/ncclRecv groups and separate reduce kernels (src/coll/*.c).
 //
 // Every rank owns a window of device memory that is bound, at the same offset,
 // to one multicast object, and sees it at two addresses: `uc` (its own copy)
 // and `mc` (all copies at once).  Layout of a window:
-//   [ kNvlsFlagBytes: one 8-byte barrier counter per CTA index, 128 bytes apart ]
-//   [ n_cta_max slots of chunk_bytes ]
-// CTA b of every rank works on chunks b, b + n_cta, ... of the message, each in five phases:
-//   1 copy the chunk from the send buffer to its slot of the own window (scaled for avg)
-//   2 barrier of the CTAs with index b of all ranks (one multimem.red on the counter, poll the own copy)
-//   3 ld_reduce the 1/n of the slot that this rank is responsible for, st the sums to all copies
-//   4 barrier
-//   5 copy the slot to the receive buffer
-// A pipelined variant (PICCL_NVLS_PIPE=1) splits the slot in two halves and overlaps the copy-in of the next chunk with
-// the switch phase of the current one; see the kernel.
-// Barrier counters only ever grow (n per barrier), over the life of the communicator.
-// Every poll is bounded: on a time-out the CTA records a status, raises the abort flag and leaves.
+//   [ kNvlsFlagBytes: counters, three per (CTA index, half slot), 128 bytes apart ]
+//   [ one slot of slot_bytes per CTA index, used as two half slots ]
+// CTA b of every rank works on chunks b, b + n_cta, ... of the message; chunk j of a CTA goes
+// through half slot j & 1, so that the next chunk is staged while the current one is in the switch.
+// One use of a half slot has up to three stages, each closed by one counter that every rank
+// raises (by n in total) on all copies with a single multimem.red:
+//   FILLED    the chunk is in the half slot   (all-reduce, reduce-scatter, reduce: every rank copied its own
+//             data into its own copy; all-gather: every rank stored its piece into every copy with
+//             multimem.st; broadcast: the root stored the chunk into every copy)
+//   REDUCED   all-reduce only: every rank has summed its 1/n of the chunk in the switch and stored the
+//             sums into every copy
+//   CONSUMED  nobody reads this use of the half slot any more (all-reduce, all-gather, broadcast: copied
+//             out; reduce-scatter / reduce: the multimem.ld_reduce that wrote the result straight to the
+//             receive buffer is done)
+// Nobody writes into a half slot before CONSUMED of its previous use is complete, whichever
+// collective that use belonged to, so calls of different collectives may follow each other freely.
+// Counters only ever grow, over the life of the communicator; the number of uses so far is kept
+// in device memory, so a captured graph can be replayed.  Every poll is bounded: on a time-out
+// the CTA records a status, raises the abort flag and leaves.
+//
+// For tests on one GPU the same kernels run with the switch emulated: all ranks are virtual ranks
+// of one cooperative launch, a load-reduce is a loop over the ranks' windows, a multicast store a
+// loop of stores (template parameter EMU).
 #pragma once
 #include <cstdint>
 #include "../include/piccl.h"
+#include "exec.cuh"
 
 namespace piccl {
 
-constexpr int kNvlsFlagBytes = 131072;
-constexpr int kNvlsMaxCta = 256;          // counters of the plain kernel: [0, 32 KiB)
-constexpr int kNvlsPipeFlagOff = 32768;   // counters of the pipelined kernel: 4 per CTA index, [32 KiB, 96 KiB)
-constexpr int kNvlsPipeMaxCta = 128;
-constexpr int kNvlsBarCounts = kNvlsMaxCta + 2 * kNvlsPipeMaxCta;   // entries of NvlsArgs::bar_count
+constexpr int kNvlsMaxCta = 128;
+constexpr int kNvlsFlagBytes = 131072;    // 128 CTA indices x 2 half slots x 3 counters x 128 bytes = 96 KiB, rounded up
 constexpr int kNvlsBlock = 512;
+constexpr int kNvlsUsedPerCta = 4;        // uses so far per CTA index: FILLED/CONSUMED of half slot 0, 1; REDUCED of half slot 0, 1
+enum NvlsCounter : int { NVC_FILLED = 0, NVC_REDUCED = 1, NVC_CONSUMED = 2 };
 
-struct NvlsArgs {
-  char* uc; char* mc;                     // the window: own copy / all copies
+struct NvlsRank {
+  char* uc; char* mc;                     // the window: own copy / all copies (mc unused when the switch is emulated)
   const void* in; void* out;
-  long long bytes;                        // message size
-  long long chunk_bytes;                  // bytes of the message per chunk, multiple of 16 * nranks, <= slot_bytes
-  long long slot_bytes;                   // distance between two slots of the window
-  int rank, nranks, n_cta, avg;
-  int pipelined;                          // 0: one chunk in flight per CTA; 1: two half slots, copy-in overlapped with the switch phase (n_cta <= kNvlsPipeMaxCta)
-  float scale;
-  unsigned long long timeout_ns;
-  unsigned long long* bar_count;          // [kNvlsBarCounts] device memory: barriers passed per CTA index (plain kernel), then uses of each half slot (pipelined)
+  unsigned long long* used;               // [kNvlsMaxCta * kNvlsUsedPerCta] device memory of this rank
   int* abort_flag;
   piccl_status_t* status;
+  int rank, pad;
 };
 
-// dtype: DT_F16, DT_F32 or DT_BF16 (exec.cuh); sum only.  Returns cudaSuccess or the launch error.
-int nvls_launch(const NvlsArgs& a, int dtype, void* stream);
-bool nvls_dtype_supported(int dtype);
+struct NvlsArgs {
+  int coll, nranks, n_cta, n_vrank;
+  int avg, root;
+  float scale;
+  int pad;
+  long long bytes;                        // all-reduce, broadcast, reduce: message bytes; all-gather, reduce-scatter: bytes of one rank's block
+  long long chunk_bytes;                  // bytes of the message (or of each rank's block) per chunk; a multiple of 16, of 16 * nranks for all-reduce
+  long long sub_stride;                   // all-gather, reduce-scatter: distance between two ranks' pieces inside a half slot (>= chunk_bytes, multiple of 16)
+  long long slot_bytes;                   // distance between two slots; a half slot is slot_bytes / 2 (multiple of 16)
+  unsigned long long timeout_ns;
+  NvlsRank r[kMaxVRanks];
+};
+
+// dtype: DT_F32 (sum), DT_F16 / DT_BF16 (sum, max, min); op as ncclRedOp_t (0 sum, 2 max, 3 min).
+// Copy-only collectives (all-gather, broadcast) use any supported pair.  emulate: virtual ranks on one device, cooperative launch.
+bool nvls_kernel_exists(int dtype, int op);
+int nvls_launch(const NvlsArgs& a, int dtype, int op, bool emulate, void* stream);
+int nvls_max_resident_ctas(bool emulate);   // co-resident CTAs of the kernel on the current device (for the cooperative launch)
 
 }  // namespace piccl

@@ -179,25 +179,56 @@ int piccl_comm_connect(piccl_comm_t* c, const piccl_handle_t* all) {
   }
   CUDA_TRY(cudaMemcpy(c->d_ctx, &c->h_ctx, sizeof(RankCtx), cudaMemcpyHostToDevice));
   c->connected = true;
-  {
-    // In-switch all-reduce: only if every rank asked for it and can do it, and no two ranks share a process
+  if (c->nranks >= 2) {
+    // In-switch collectives: a multicast window if every rank asked for it and can do it, and no two ranks share a process
     // (each rank binds its own device to the multicast object, and the set-up blocks until all ranks take part).
-    bool want = true; int root_pid = 0; unsigned long long root_id = 0;
+    // All ranks inside this process on this device (virtual ranks): a plain window each, the kernels emulate the switch.
+    bool want = true, one_process = true; int root_pid = 0; unsigned long long root_id = 0;
     for (int p = 0; p < c->nranks; p++) {
       HandleBlob b; memcpy(&b, all[p].bytes, sizeof b);
       want &= (b.ipc_ok & 2) != 0;
+      one_process &= b.pid == (int)getpid() && b.device == c->device;
       if (p == 0) { root_pid = b.pid; root_id = b.raw_ptr; }
       for (int q = 0; q < p; q++) { HandleBlob o; memcpy(&o, all[q].bytes, sizeof o); if (o.pid == b.pid) want = false; }
     }
-    if (want) nvls_setup(c, root_pid, root_id);
+    if (one_process) { if (env().nvls && c->nranks <= kMaxVRanks) nvls_setup_emulated(c); }
+    else if (want) nvls_setup(c, root_pid, root_id);
   }
   return PICCL_OK;
+}
+
+// A consumer's kernel acknowledges the last entries this rank sent by writing head counters into THIS rank's heap, and that
+// can happen after this rank's own kernels have ended.  Before the heap is freed: wait on the host, with a limit, until every
+// entry sent has been acknowledged.  (Everything peers sent to this rank was consumed by kernels that have ended.)
+static void quiesce_fifos(piccl_comm* c) {
+  if (!c->connected || !c->heap || c->nranks < 2 || c->broken || (c->h_status && c->h_status->aborted)) return;
+  const RankCtx& x = c->h_ctx;
+  const int n = c->nranks, mc = c->cfg.max_cta;
+  std::vector<unsigned long long> sent((size_t)n * mc), sent_ll((size_t)n * kLLFifoCta);
+  const size_t head_bytes = (size_t)n * mc * kFlagStride, llh_bytes = (size_t)n * kLLFifoCta * kFlagStride;
+  std::vector<char> head(head_bytes), llh(llh_bytes);
+  if (cudaMemcpy(sent.data(), c->d_sent, sent.size() * 8, cudaMemcpyDeviceToHost) != cudaSuccess ||
+      cudaMemcpy(sent_ll.data(), c->d_sent_ll, sent_ll.size() * 8, cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return; }
+  for (int tries = 0; tries < 200; tries++) {
+    if (cudaMemcpy(head.data(), c->heap + x.head_off, head_bytes, cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemcpy(llh.data(), c->heap + x.llf_head_off, llh_bytes, cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return; }
+    bool done = true;
+    for (int p = 0; p < n && done; p++) {
+      if (p == c->rank) continue;
+      for (int b = 0; b < mc && done; b++) { unsigned long long h; memcpy(&h, &head[(size_t)(p * mc + b) * kFlagStride], 8); if (h < sent[(size_t)p * mc + b]) done = false; }
+      for (int b = 0; b < kLLFifoCta && done; b++) { unsigned long long h; memcpy(&h, &llh[(size_t)(p * kLLFifoCta + b) * kFlagStride], 8); if (h < sent_ll[(size_t)p * kLLFifoCta + b]) done = false; }
+    }
+    if (done) return;
+    usleep(5000);
+  }
+  log_msg(1, "rank %d: peers did not acknowledge everything this rank sent within 1 s", c->rank);
 }
 
 int piccl_comm_destroy(piccl_comm_t* c) {
   if (!c) return PICCL_OK;
   DevGuard g(c->device);
   cudaDeviceSynchronize();
+  quiesce_fifos(c);
   persist_destroy(c);
   nvls_destroy(c);
   if (!env().trace_file.empty()) trace_dump(c);
@@ -431,16 +462,35 @@ static int run(piccl_comm** comms, int n, const CallDesc* calls, cudaStream_t st
     }
   }
 
-  // all-reduce summed inside the switch (sum / avg of fp32, fp16, bf16; one communicator per launch); anything else runs the ring
-  if ((d0.algo == ALGO_NVLS || env().proto == 3) && d0.coll == COLL_ALLREDUCE && n == 1 && op == 0 && nvls_ready(c0) && nvls_dtype_supported(d0.dtype)) {
-    std::lock_guard<std::mutex> l(c0->mu);
-    const bool skip = fault_now(c0); c0->call_index++;
-    if (skip) return PICCL_OK;
-    TraceRec* tr = trace_begin(c0, d0.coll, d0.algo, 0, (long long)d0.count * esz_real, 0, stream);
-    int rc = nvls_allreduce(c0, d0.send, d0.recv, d0.count, d0.dtype, avg, stream);
-    trace_end(c0, tr, stream);
-    if (rc == PICCL_OK) { c0->stats.launches++; c0->stats.nvls_calls++; c0->stats.calls[COLL_ALLREDUCE]++; c0->stats.bytes[COLL_ALLREDUCE] += (unsigned long long)d0.count * esz_real; }
-    return rc;
+  // through the switch: all ranks of the communicator in this launch (one real rank, or every virtual rank of an emulated group)
+  if (d0.algo == ALGO_NVLS || env().proto == 3) {
+    bool can = (op == 0 || op == 2 || op == 3 || !reducing) && (n == 1 ? !nvls_emulated(c0) : nvls_emulated(c0) && n == c0->nranks);
+    for (int i = 0; i < n && can; i++) can = nvls_eligible(comms[i], d0.coll, d0.dtype, op, d0.count);
+    if (can) {
+      bool skip = false;
+      for (int i = 0; i < n; i++) { std::lock_guard<std::mutex> l(comms[i]->mu); skip |= fault_now(comms[i]); comms[i]->call_index++; }
+      if (skip) return PICCL_OK;
+      const void* ins[kMaxVRanks]; void* outs[kMaxVRanks];
+      for (int i = 0; i < n; i++) { ins[i] = calls[i].send; outs[i] = calls[i].recv; }
+      TraceRec* tr = trace_begin(c0, d0.coll, ALGO_NVLS, 0, (long long)d0.count * esz_real, 0, stream);
+      nvtxRangePushA("in_switch");
+      int rc = nvls_collective(comms, n, d0.coll, ins, outs, d0.count, d0.dtype, op, avg, d0.root, stream);
+      nvtxRangePop();
+      trace_end(c0, tr, stream);
+      if (rc == PICCL_OK) {
+        for (int i = 0; i < n; i++) { piccl_comm* c = comms[i]; c->stats.launches++; c->stats.nvls_calls++; c->stats.calls[d0.coll]++; c->stats.bytes[d0.coll] += (unsigned long long)d0.count * esz_real; }
+        return rc;
+      }
+      if (rc != PICCL_UNSUPPORTED) return rc;
+    }
+  }
+  if (d0.algo == ALGO_NVLS) {
+    // no window, or a type / operator / size the switch path does not take: what AUTO picks without a window
+    CallDesc alt[kMaxVRanks];
+    int k2 = d0.k;
+    const Algo a2 = select_algo_p2p(c0, d0.coll, d0.count * (size_t)esz_real, &k2);
+    for (int i = 0; i < n; i++) { alt[i] = calls[i]; alt[i].algo = a2; alt[i].k = k2; }
+    return run(comms, n, alt, stream);
   }
 
   // slabs: bound the local scratch of the recursive reduce-scatters

@@ -75,7 +75,9 @@ void trace_end(piccl_comm* c, TraceRec* r, cudaStream_t s);
 void trace_dump(piccl_comm* c);
 // Algorithm choice for AUTO / unspecified requests: PICCL_TUNE_FILE table if given, else built-in thresholds.
 Algo select_algo(piccl_comm* c, Coll coll, size_t bytes, int* k);
-Algo select_algo_n(int nranks, Coll coll, size_t bytes, int* k);
+Algo select_algo_n(int nranks, Coll coll, size_t bytes, int* k, bool window);
+// the rule for a communicator without a multicast window (what an NVLS request falls back to)
+Algo select_algo_p2p(piccl_comm* c, Coll coll, size_t bytes, int* k);
 // persistent launcher (PICCL_LAUNCH=persistent): PICCL_OK if enqueued through the server, PICCL_UNSUPPORTED: launch directly
 int persist_allreduce(piccl_comm** cs, int n, const LLArgs& la, const void* const* in, void* const* out, long long count, int dtype, int op, int avg,
                       int algo, int k, cudaStream_t stream);

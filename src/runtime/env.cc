@@ -42,16 +42,17 @@ static void load() {
   e.tp_mb = env_int("PICCL_TP_MB", 0);           // heap space for the fused tensor-parallel kernels (0: none)
   e.tp_feeders = env_int("PICCL_TP_FEEDERS", 24); // CTAs that push the local shard in all-gather -> GEMM
   e.exec_defer = env_int("PICCL_EXEC_DEFER", 0);
-  e.nvls = env_int("PICCL_NVLS", 0);            // 1: build an NVLink multicast window per communicator (algorithm NVLS)
-  e.nvls_chunk_kb = env_int("PICCL_NVLS_CHUNK_KB", 256);
-  e.nvls_cta = env_int("PICCL_NVLS_CTA", 64);
+  e.nvls = env_int("PICCL_NVLS", 1);            // 0: no NVLink multicast window (algorithm NVLS then runs the peer-to-peer schedules)
+  e.nvls_chunk_kb = env_int("PICCL_NVLS_CHUNK_KB", 256);   // half slot = largest chunk one CTA has in the switch at a time
+  e.nvls_cta = env_int("PICCL_NVLS_CTA", 64);              // CTAs (= slots of the window) of an in-switch collective
+  e.nvls_auto_kb = env_int("PICCL_NVLS_AUTO_KB", 256);     // AUTO sends messages above this size through the switch when a window exists
+  e.nvls_min_kb = env_int("PICCL_NVLS_MIN_KB", 64);        // a mid-size message is cut into chunks of at least this size before more CTAs are used
   { const char* g = getenv("PICCL_NVLS_GRAN"); e.nvls_gran_min = g && !strcmp(g, "min"); }
-  e.nvls_pipe = env_int("PICCL_NVLS_PIPE", 0);   // 1: the pipelined kernel (two half slots per CTA)
   // PICCL_PROTO narrows the choice of data path that is otherwise made per call by message size:
   //   auto    (default) low-latency kernels for small messages, the FIFO executor otherwise
   //   simple  FIFO executor only
   //   ll      low-latency executor up to 1 MiB for every collective
-  //   nvls    builds the multicast window and sums every eligible all-reduce (sum / avg of fp32, fp16, bf16) inside the switch
+  //   nvls    every eligible collective goes through the switch, whatever its size
   e.proto = 0;
   if (const char* p = getenv("PICCL_PROTO")) {
     if (!strcmp(p, "ll")) { e.proto = 1; e.llf_kb = std::max(e.llf_kb, 1024); }
@@ -94,9 +95,9 @@ extern "C" int piccl_env_describe(char* buf, int len) {
   const piccl::Env& e = piccl::env();
   static const char* proto[] = {"auto", "ll", "simple", "nvls"};
   return snprintf(buf, len > 0 ? (size_t)len : 0,
-                  "proto=%s ll_kb=%d llf_kb=%d nvls=%d nvls_chunk_kb=%d nvls_cta=%d nvls_pipe=%d max_cta=%d slot_kb=%d nslot=%d timeout_ms=%d "
+                  "proto=%s ll_kb=%d llf_kb=%d nvls=%d nvls_chunk_kb=%d nvls_cta=%d nvls_min_kb=%d max_cta=%d slot_kb=%d nslot=%d timeout_ms=%d "
                   "launch=%s allreduce=%s/%d allgather=%s/%d broadcast=%s/%d reduce=%s/%d reduce_scatter=%s/%d",
-                  proto[e.proto & 3], e.ll_kb, e.llf_kb, e.nvls, e.nvls_chunk_kb, e.nvls_cta, e.nvls_pipe, e.max_cta, e.slot_kb, e.nslot, e.timeout_ms,
+                  proto[e.proto & 3], e.ll_kb, e.llf_kb, e.nvls, e.nvls_chunk_kb, e.nvls_cta, e.nvls_min_kb, e.max_cta, e.slot_kb, e.nslot, e.timeout_ms,
                   e.launch_persistent ? "persistent" : "direct", piccl::algo_name(e.algo[piccl::COLL_ALLREDUCE]), e.k[piccl::COLL_ALLREDUCE],
                   piccl::algo_name(e.algo[piccl::COLL_ALLGATHER]), e.k[piccl::COLL_ALLGATHER], piccl::algo_name(e.algo[piccl::COLL_BROADCAST]), e.k[piccl::COLL_BROADCAST],
                   piccl::algo_name(e.algo[piccl::COLL_REDUCE]), e.k[piccl::COLL_REDUCE], piccl::algo_name(e.algo[piccl::COLL_REDUCE_SCATTER]), e.k[piccl::COLL_REDUCE_SCATTER]);

@@ -1,14 +1,17 @@
-// Host side of the in-switch all-reduce (kernel: kernels/nvls_allreduce.cu): the
-// multicast window of a communicator.  Opt-in (PICCL_NVLS=1); the algorithm name is NVLS.
+// Host side of the in-switch collectives (kernels: kernels/nvls_coll.cu): the multicast
+// window of a communicator and the launch geometry.  PICCL_NVLS=0 turns the window off;
+// the algorithm name is NVLS and AUTO picks it for large messages when a window exists.
 //
 // Set-up, inside piccl_comm_connect once every rank's handle is known:
 //   rank 0 creates the multicast object and exports it as a file descriptor; the
 //   descriptor travels to the peers over a Unix socket (fdshare.h); every rank adds
 //   its device; barrier; every rank creates device memory of the window size, binds it
 //   to the object at offset 0, maps its own copy (uc) and the multicast view (mc),
-//   clears the barrier counters; barrier.  A failure on any rank makes all ranks drop
+//   clears the counters; barrier.  A failure on any rank makes all ranks drop
 //   the window again (the barriers carry the verdict) and the communicator works
-//   without it: NVLS requests then run the ring.
+//   without it: NVLS requests then run the peer-to-peer schedules.
+// When all ranks of a communicator are virtual ranks of one process on one device the window is
+// plain device memory and the kernels emulate the switch (tests on one GPU).
 // The driver entry points are fetched at run time, so the library links against the
 // CUDA runtime only.  The reference has no counterpart.
 #include <cuda.h>
@@ -77,7 +80,8 @@ struct NvlsState {
   CUdeviceptr uc_va = 0, mc_va = 0;
   size_t win = 0;
   long long slot_bytes = 0; int max_cta = 0;
-  unsigned long long* d_bar = nullptr;
+  unsigned long long* d_used = nullptr;      // uses of every half slot so far (kernels/nvls.cuh)
+  bool emulated = false; char* emu_win = nullptr;
 };
 
 void teardown(NvlsState* s) {
@@ -89,7 +93,8 @@ void teardown(NvlsState* s) {
   if (s->uc_va) { d.MemAddressFree(s->uc_va, s->win); s->uc_va = 0; }
   if (s->have_mem) { d.MemRelease(s->mem); s->have_mem = false; }
   if (s->have_mc) { d.MemRelease(s->mc); s->have_mc = false; }
-  if (s->d_bar) { cudaFree(s->d_bar); s->d_bar = nullptr; }
+  if (s->d_used) { cudaFree(s->d_used); s->d_used = nullptr; }
+  if (s->emu_win) { cudaFree(s->emu_win); s->emu_win = nullptr; }
   s->ready = false;
 }
 
@@ -120,10 +125,59 @@ bool nvls_device_capable(int device) {
 }
 
 bool nvls_ready(const piccl_comm* c) { return c->nvls && static_cast<const NvlsState*>(c->nvls)->ready; }
+bool nvls_emulated(const piccl_comm* c) { return nvls_ready(c) && static_cast<const NvlsState*>(c->nvls)->emulated; }
+
+static void window_geometry(NvlsState* s, bool emulated) {
+  const Env& e = env();
+  s->max_cta = std::max(1, std::min(e.nvls_cta, emulated ? 32 : kNvlsMaxCta));
+  s->slot_bytes = 2 * std::max<long long>(1, e.nvls_chunk_kb) * 1024;     // two half slots of PICCL_NVLS_CHUNK_KB
+  s->slot_bytes = (s->slot_bytes + 4095) / 4096 * 4096;
+}
+
+// All ranks are virtual ranks of this process on this device: plain memory, the kernels loop over the ranks' windows.
+void nvls_setup_emulated(piccl_comm* c) {
+  NvlsState* s = new NvlsState();
+  c->nvls = s;
+  window_geometry(s, true);
+  s->emulated = true;
+  s->win = (size_t)kNvlsFlagBytes + (size_t)s->max_cta * (size_t)s->slot_bytes;
+  cudaError_t ce = cudaMalloc(&s->emu_win, s->win);
+  if (ce == cudaSuccess) ce = cudaMemset(s->emu_win, 0, kNvlsFlagBytes);
+  if (ce == cudaSuccess) ce = cudaMalloc(&s->d_used, (size_t)kNvlsMaxCta * kNvlsUsedPerCta * sizeof(unsigned long long));
+  if (ce == cudaSuccess) ce = cudaMemset(s->d_used, 0, (size_t)kNvlsMaxCta * kNvlsUsedPerCta * sizeof(unsigned long long));
+  if (ce == cudaSuccess) ce = cudaDeviceSynchronize();
+  if (ce != cudaSuccess) { cudaGetLastError(); log_msg(1, "rank %d: no emulated window (%s)", c->rank, cudaGetErrorString(ce)); teardown(s); return; }
+  s->uc_va = (CUdeviceptr)(uintptr_t)s->emu_win;
+  s->ready = true;
+}
+
+// Before the window goes away: arrivals of the peers for this rank's last uses of each half slot may still be on their
+// way (they are the last thing a peer's kernel does).  Waits on the host, with a limit, until every CONSUMED counter shows
+// all ranks; nothing writes into the window after that.
+static void quiesce(piccl_comm* c, NvlsState* s) {
+  if (!s->ready || s->emulated || !s->d_used) return;
+  const size_t nu = (size_t)kNvlsMaxCta * kNvlsUsedPerCta;
+  std::vector<unsigned long long> used(nu), flags(kNvlsFlagBytes / sizeof(unsigned long long));
+  if (cudaMemcpy(used.data(), s->d_used, nu * sizeof(unsigned long long), cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return; }
+  for (int tries = 0; tries < 200; tries++) {
+    if (cudaMemcpy(flags.data(), (const void*)s->uc_va, kNvlsFlagBytes, cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return; }
+    bool done = true;
+    for (int b = 0; b < kNvlsMaxCta && done; b++)
+      for (int h = 0; h < 2; h++) {
+        const unsigned long long want = used[(size_t)b * kNvlsUsedPerCta + h] * (unsigned long long)c->nranks;
+        const unsigned long long have = flags[(size_t)(((b * 2 + h) * 3 + NVC_CONSUMED) * 128) / sizeof(unsigned long long)];
+        if (have < want) { done = false; break; }
+      }
+    if (done) return;
+    usleep(5000);
+  }
+  log_msg(1, "rank %d: peers did not finish with the multicast window within 1 s", c->rank);
+}
 
 void nvls_destroy(piccl_comm* c) {
   if (!c->nvls) return;
   NvlsState* s = static_cast<NvlsState*>(c->nvls);
+  quiesce(c, s);
   teardown(s);
   delete s;
   c->nvls = nullptr;
@@ -143,9 +197,7 @@ void nvls_setup(piccl_comm* c, int root_pid, unsigned long long root_id) {
   STEP(d.CtxGetDevice(&s->dev));
 
   // window geometry: the same arithmetic on every rank
-  s->max_cta = std::max(1, std::min(e.nvls_cta, kNvlsMaxCta));
-  s->slot_bytes = std::max<long long>(1, e.nvls_chunk_kb) * 1024;
-  s->slot_bytes = (s->slot_bytes + 16LL * n - 1) / (16LL * n) * (16LL * n);
+  window_geometry(s, false);
   size_t want = (size_t)kNvlsFlagBytes + (size_t)s->max_cta * (size_t)s->slot_bytes;
   CUmulticastObjectProp mp; memset(&mp, 0, sizeof mp);
   mp.numDevices = (unsigned)n; mp.size = want; mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
@@ -205,8 +257,8 @@ void nvls_setup(piccl_comm* c, int root_pid, unsigned long long root_id) {
 #undef STEP
   if (ok) {
     cudaError_t ce = cudaMemset((void*)s->uc_va, 0, kNvlsFlagBytes);
-    if (ce == cudaSuccess) ce = cudaMalloc(&s->d_bar, kNvlsBarCounts * sizeof(unsigned long long));
-    if (ce == cudaSuccess) ce = cudaMemset(s->d_bar, 0, kNvlsBarCounts * sizeof(unsigned long long));
+    if (ce == cudaSuccess) ce = cudaMalloc(&s->d_used, (size_t)kNvlsMaxCta * kNvlsUsedPerCta * sizeof(unsigned long long));
+    if (ce == cudaSuccess) ce = cudaMemset(s->d_used, 0, (size_t)kNvlsMaxCta * kNvlsUsedPerCta * sizeof(unsigned long long));
     if (ce == cudaSuccess) ce = cudaDeviceSynchronize();
     if (ce != cudaSuccess) { cudaGetLastError(); ok = false; snprintf(why, sizeof why, "clearing the window: %s", cudaGetErrorString(ce)); }
   }
@@ -215,7 +267,7 @@ void nvls_setup(piccl_comm* c, int root_pid, unsigned long long root_id) {
   if (ok && !all) { ok = false; snprintf(why, sizeof why, "another rank could not bind its window"); }
   fdshare_close(sh);
   if (!ok) {
-    log_msg(1, "rank %d: no multicast window (%s); NVLS requests run the ring", c->rank, why);
+    log_msg(1, "rank %d: no multicast window (%s); NVLS requests run the peer-to-peer schedules", c->rank, why);
     teardown(s);
     return;
   }
@@ -223,30 +275,63 @@ void nvls_setup(piccl_comm* c, int root_pid, unsigned long long root_id) {
   log_msg(1, "rank %d: multicast window of %.1f MiB (%d slots of %lld KiB)", c->rank, s->win / 1048576.0, s->max_cta, s->slot_bytes >> 10);
 }
 
-int nvls_allreduce(piccl_comm* c, const void* in, void* out, size_t count, int dtype, bool avg, cudaStream_t stream) {
-  if (!nvls_ready(c) || !nvls_dtype_supported(dtype)) return PICCL_UNSUPPORTED;
-  NvlsState* s = static_cast<NvlsState*>(c->nvls);
-  const long long bytes = (long long)count * dtype_size(dtype);
-  const long long unit = 16LL * c->nranks;
+// What the kernels take: sum of fp32, sum / max / min of fp16 and bf16 (what the switch can reduce), any type for the
+// collectives that only move data; messages (blocks) of a multiple of 16 bytes except for all-reduce, which stages through
+// typed copies.  Only what is the same on every rank may decide (never a buffer address): all ranks must take the same path.
+bool nvls_eligible(const piccl_comm* c, int coll, int dtype, int op, size_t count) {
+  if (!nvls_ready(c) || count == 0) return false;
+  const long long es = dtype_size(dtype);
+  if (!es) return false;
+  const bool reducing = coll == COLL_ALLREDUCE || coll == COLL_REDUCE || coll == COLL_REDUCE_SCATTER;
+  if (reducing && !nvls_kernel_exists(dtype, op)) return false;
+  const long long bytes = (long long)count * es;
+  if (bytes >= (1LL << 40)) return false;
+  if (coll == COLL_ALLREDUCE) return true;
+  return (bytes & 15) == 0;
+}
+
+// Enqueues one collective on `n` communicators: n == 1, the normal case, or all virtual ranks of an emulated group.
+// op: 0 sum, 2 max, 3 min (avg: sum with `avg` set).  count: elements of the message, or of one rank's block for
+// all-gather / reduce-scatter.  Callers check nvls_eligible first.
+int nvls_collective(piccl_comm** comms, int n, int coll, const void* const* in, void* const* out, size_t count, int dtype, int op, bool avg, int root, cudaStream_t stream) {
+  piccl_comm* c0 = comms[0];
+  NvlsState* s0 = static_cast<NvlsState*>(c0->nvls);
+  const bool emu = s0->emulated;
+  if (emu ? n != c0->nranks : n != 1) return PICCL_UNSUPPORTED;
+  const int nr = c0->nranks;
+  const long long es = dtype_size(dtype), bytes = (long long)count * es, half = s0->slot_bytes / 2;
+  const bool blocks = coll == COLL_ALLGATHER || coll == COLL_REDUCE_SCATTER;      // the message is one block per rank
+  const bool reducing = coll == COLL_ALLREDUCE || coll == COLL_REDUCE || coll == COLL_REDUCE_SCATTER;
   NvlsArgs a; memset(&a, 0, sizeof a);
-  a.uc = (char*)s->uc_va; a.mc = (char*)s->mc_va; a.in = in; a.out = out; a.bytes = bytes;
-  // mid-size messages are spread over all CTAs instead of filling a few slots
-  long long chunk = (bytes + s->max_cta - 1) / s->max_cta;
-  chunk = std::max<long long>(chunk, 16384);
-  chunk = (chunk + unit - 1) / unit * unit;
-  a.pipelined = env().nvls_pipe ? 1 : 0;
-  const int max_cta = a.pipelined ? std::min(s->max_cta, kNvlsPipeMaxCta) : s->max_cta;
-  const long long room = a.pipelined ? (s->slot_bytes / 2) / unit * unit : s->slot_bytes;      // a chunk fills a slot, or half of it
+  a.coll = coll; a.nranks = nr; a.n_vrank = n; a.avg = (avg && reducing) ? 1 : 0; a.root = root; a.scale = a.avg ? 1.0f / (float)nr : 1.0f;
+  a.bytes = bytes; a.slot_bytes = s0->slot_bytes;
+  a.timeout_ns = (unsigned long long)c0->cfg.timeout_ms * 1000000ull;
+  // chunks: spread a mid-size message over all CTAs (at least PICCL_NVLS_MIN_KB of traffic per chunk), fill the half slots for a large one
+  const long long unit = coll == COLL_ALLREDUCE ? 16LL * nr : 16;
+  const long long room = blocks ? (half / nr) / 16 * 16 : half / unit * unit;       // largest chunk (per rank block for all-gather / reduce-scatter)
   if (room < unit) return PICCL_UNSUPPORTED;
+  a.sub_stride = blocks ? room : 0;
+  int max_cta = s0->max_cta;
+  if (emu) max_cta = std::max(1, std::min(max_cta, nvls_max_resident_ctas(true) / n));
+  const long long total = blocks ? bytes * nr : bytes;
+  const long long min_chunk = std::max<long long>(1, env().nvls_min_kb) * 1024;
+  const long long want_cta = std::max<long long>(1, std::min<long long>((total + min_chunk - 1) / min_chunk, max_cta));
+  long long chunk = (bytes + want_cta - 1) / want_cta;
+  chunk = (chunk + unit - 1) / unit * unit;
   a.chunk_bytes = std::min(chunk, room);
-  a.slot_bytes = s->slot_bytes;
   const long long nchunks = (bytes + a.chunk_bytes - 1) / a.chunk_bytes;
-  a.rank = c->rank; a.nranks = c->nranks; a.n_cta = (int)std::min<long long>(nchunks, max_cta);
-  a.avg = avg ? 1 : 0; a.scale = avg ? 1.0f / (float)c->nranks : 1.0f;
-  a.timeout_ns = (unsigned long long)c->cfg.timeout_ms * 1000000ull;
-  a.bar_count = s->d_bar; a.abort_flag = c->d_abort; a.status = c->d_status;
-  cudaError_t e = (cudaError_t)nvls_launch(a, dtype, stream);
-  if (e != cudaSuccess) return fail(PICCL_CUDA_ERROR, "in-switch all-reduce launch failed: %s", cudaGetErrorString(e));
+  a.n_cta = (int)std::min<long long>(nchunks, max_cta);
+  for (int i = 0; i < n; i++) {
+    piccl_comm* c = comms[i];
+    NvlsState* s = static_cast<NvlsState*>(c->nvls);
+    if (!s || !s->ready || s->emulated != emu || s->slot_bytes != s0->slot_bytes) return PICCL_UNSUPPORTED;
+    NvlsRank& r = a.r[i];
+    r.uc = (char*)s->uc_va; r.mc = (char*)s->mc_va; r.in = in[i]; r.out = out[i]; r.used = s->d_used; r.abort_flag = c->d_abort; r.status = c->d_status; r.rank = c->rank;
+  }
+  // copy-only collectives run any instantiation
+  const int kdt = reducing ? dtype : DT_F32, kop = reducing ? op : 0;
+  cudaError_t e = (cudaError_t)nvls_launch(a, kdt, kop, emu, stream);
+  if (e != cudaSuccess) return fail(PICCL_CUDA_ERROR, "in-switch %s launch failed: %s", coll_name((Coll)coll), cudaGetErrorString(e));
   return PICCL_OK;
 }
 

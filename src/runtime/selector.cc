@@ -9,6 +9,7 @@
 #include <cstring>
 #include <mutex>
 #include "comm.h"
+#include "nvls.h"
 
 namespace piccl {
 
@@ -34,10 +35,17 @@ static void load_table() {
   log_msg(1, "tuning table %s: %zu rows", path.c_str(), g_rows.size());
 }
 
-Algo select_algo_n(int n, Coll coll, size_t bytes, int* k) {
+Algo select_algo_n(int n, Coll coll, size_t bytes, int* k, bool window) {
   std::call_once(g_once, load_table);
   for (auto& r : g_rows)
-    if (r.coll == coll && r.nranks == n && (long long)bytes <= r.max_bytes) { if (k) *k = r.k; return r.algo; }
+    if (r.coll == coll && r.nranks == n && (long long)bytes <= r.max_bytes && (window || r.algo != ALGO_NVLS)) { if (k) *k = r.k; return r.algo; }
+  // With a multicast window: everything that is not latency bound goes through the switch (the message crosses each
+  // link about once instead of 2(n-1)/n times, and no step waits for a neighbour's step).  `bytes` is the whole vector
+  // for all-reduce / broadcast / reduce and one rank's block for all-gather / reduce-scatter.
+  if (window && n >= 2) {
+    const size_t total = (coll == COLL_ALLGATHER || coll == COLL_REDUCE_SCATTER) ? bytes * (size_t)n : bytes;
+    if (total > ((size_t)env().nvls_auto_kb << 10)) { if (k) *k = -1; return ALGO_NVLS; }
+  }
   // Built-in rule, from sweeps on 2, 4 and 8 B200 (fp32 and bf16 sum):
   //   all-reduce      <= 4 KiB one exchange with every rank (PRM, k = n: 8 us on 8 GPUs); up to 32 MiB (8 MiB on two
   //                   ranks) recursive doubling, whose few steps beat the ring's 2(n-1) (222 vs 154 GB/s at 16 MiB on 8
@@ -60,16 +68,19 @@ Algo select_algo_n(int n, Coll coll, size_t bytes, int* k) {
   }
 }
 
-Algo select_algo(piccl_comm* c, Coll coll, size_t bytes, int* k) { return select_algo_n(c->nranks, coll, bytes, k); }
+Algo select_algo(piccl_comm* c, Coll coll, size_t bytes, int* k) { return select_algo_n(c->nranks, coll, bytes, k, nvls_ready(c)); }
+Algo select_algo_p2p(piccl_comm* c, Coll coll, size_t bytes, int* k) { return select_algo_n(c->nranks, coll, bytes, k, false); }
 
 }  // namespace piccl
 
 // What AUTO resolves to for a communicator of `nranks` ranks (tuning table first, then the built-in rule).
 // Returns the algorithm (PICCL_ALGO_*) and, through *k, the radix or group size (-1 / 2 / n as the rule says).
-extern "C" int piccl_select_algorithm(int nranks, int coll, unsigned long long bytes, int* k) {
+// piccl_select_algorithm answers for a communicator without a multicast window, the _ex form for either.
+extern "C" int piccl_select_algorithm_ex(int nranks, int coll, unsigned long long bytes, int have_window, int* k) {
   int kk = -1;
   if (coll < 0 || coll >= piccl::COLL_COUNT || nranks < 1) return 0;
-  piccl::Algo a = piccl::select_algo_n(nranks, (piccl::Coll)coll, (size_t)bytes, &kk);
+  piccl::Algo a = piccl::select_algo_n(nranks, (piccl::Coll)coll, (size_t)bytes, &kk, have_window != 0);
   if (k) *k = kk;
   return (int)a;
 }
+extern "C" int piccl_select_algorithm(int nranks, int coll, unsigned long long bytes, int* k) { return piccl_select_algorithm_ex(nranks, coll, bytes, 0, k); }

@@ -1,7 +1,9 @@
-"""Worker of tests/test_nvls_gpu.py: in-switch all-reduce on a communicator of ONE rank.
-The multicast object then has a single device, so sums equal the input, but every part of the path runs:
-window set-up, both views, multimem.ld_reduce / multimem.st / multimem.red, the barrier counters, chunking.
-Prints NVLS_UNAVAILABLE when the driver gives no multicast window, NVLS_OK on success."""
+"""Worker of tests/test_nvls_gpu.py: the in-switch collectives (algorithm NVLS) with the switch EMULATED on one GPU.
+All ranks are virtual ranks of one cooperative launch (LoopbackGroup); a multimem load-reduce becomes a loop over the
+ranks' windows and a multicast store a loop of stores, everything else (chunking, half slots, counters, copies, the
+handling of unaligned buffers and odd sizes) is the code that runs on real NVLink multicast windows.  Results are
+compared with plain PyTorch fp32 arithmetic.  Small half slots (PICCL_NVLS_CHUNK_KB) make every CTA wrap around its two
+half slots many times, and the collectives are interleaved so that a half slot is reused by a different collective."""
 import os
 import sys
 from pathlib import Path
@@ -9,65 +11,141 @@ from pathlib import Path
 import torch
 
 sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
-os.environ["PICCL_NVLS"] = "1"
-os.environ.setdefault("PICCL_LOG", "1")
+os.environ.setdefault("PICCL_NVLS", "1")
+os.environ.setdefault("PICCL_NVLS_CHUNK_KB", "8")
+os.environ.setdefault("PICCL_NVLS_MIN_KB", "4")
+os.environ.setdefault("PICCL_NVLS_CTA", "6")
+
+
+def rand(count, dtype, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.rand(count, generator=g, device="cuda") * 2 - 1).to(dtype)
+
+
+def tol(dtype, n):
+    return {torch.float32: 2e-6 * n, torch.bfloat16: 1.6e-2 * n ** 0.5, torch.float16: 2e-3 * n ** 0.5}[dtype]
+
+
+def reduce_ref(xs, op):
+    st = torch.stack([x.float() for x in xs])
+    return {"sum": st.sum(0), "avg": st.mean(0), "max": st.max(0).values, "min": st.min(0).values}[op]
 
 
 def main():
-    from piccl_b200.parallel.comm import Communicator, make_config
+    from piccl_b200.parallel.comm import LoopbackGroup, make_config
     torch.cuda.set_device(0)
-    comm = Communicator(rank=0, nranks=1, device=0, config=make_config(timeout_ms=2000))
-    probe = torch.ones(1024, device="cuda")
-    comm.all_reduce(probe, algo="NVLS")
-    torch.cuda.synchronize()
-    if comm.stats().nvls_calls == 0:
-        print("NVLS_UNAVAILABLE")
-        return
-    calls = 1
-    g = torch.Generator(device="cuda").manual_seed(1)
-    for dtype in (torch.float32, torch.bfloat16, torch.float16):
-        # 1000: one partial chunk; 1 MiB + 3: a tail that is not a multiple of 16 bytes; 40 Mi elements: several chunks per CTA
-        for count in (1, 1000, (1 << 20) + 3, 40 << 20):
-            x = (torch.rand(count, generator=g, device="cuda") * 2 - 1).to(dtype)
-            out = torch.empty_like(x)
-            comm.all_reduce(x, out, algo="NVLS")
-            calls += 1
+    expected_switch_calls = 0
+    for n in (2, 3, 8):
+        grp = LoopbackGroup(n, config=make_config(max_cta=4, timeout_ms=4000))
+        before = grp.stats().nvls_calls
+
+        def healthy(what):
             torch.cuda.synchronize()
-            st = comm.status()
-            assert st.aborted == 0, f"wait gave up: code {st.code} cta {st.cta} chunk {st.segment} want {st.want} have {st.have}"
-            assert torch.equal(out, x), f"{dtype} {count}: {(out.float() - x.float()).abs().max().item()}"
-        # in place, unaligned start, avg (scale 1/1)
-        base = (torch.rand(70001, generator=g, device="cuda") * 2 - 1).to(dtype)
-        y = base[1:]                      # starts 2 or 4 bytes past a 16-byte boundary: element-wise copies
-        want = y.clone()
-        comm.all_reduce(y, op="avg", algo="NVLS")
-        calls += 1
-        torch.cuda.synchronize()
-        assert torch.equal(y, want), f"{dtype} in place"
-    # unsupported type: the request runs the ring schedule instead
-    z = torch.arange(5000, device="cuda", dtype=torch.int32)
-    comm.all_reduce(z, algo="NVLS")
-    torch.cuda.synchronize()
-    assert torch.equal(z, torch.arange(5000, device="cuda", dtype=torch.int32))
-    assert comm.stats().nvls_calls == calls, (comm.stats().nvls_calls, calls)
-    # replay from a CUDA graph: the barrier counters live in device memory
-    x = torch.randn(1 << 20, device="cuda")
-    out = torch.empty_like(x)
-    s = torch.cuda.Stream()
-    with torch.cuda.stream(s):
-        comm.all_reduce(x, out, algo="NVLS", stream=s)
-        s.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=s):
-            comm.all_reduce(x, out, algo="NVLS", stream=s)
-        for i in range(3):
-            x.fill_(float(i))
-            graph.replay()
-            s.synchronize()
-            assert torch.equal(out, x)
-    assert comm.status().aborted == 0
-    comm.close()
-    print("NVLS_OK")
+            st = grp.status()
+            assert st.aborted == 0, f"{what}: wait gave up: code {st.code} rank {st.rank} cta {st.cta} chunk {st.segment} want {st.want} have {st.have}"
+
+        calls = 0
+        for dtype in (torch.float32, torch.bfloat16, torch.float16):
+            es = torch.empty(0, dtype=dtype).element_size()
+            ops = ("sum", "avg") if dtype == torch.float32 else ("sum", "avg", "max", "min")
+            # element counts: one element; an odd size with a tail; several chunks per CTA (6 CTAs x 2 half slots of 8 KiB)
+            for count in (1, 1001, (200 * 1024) // es + 3):
+                for op in ops:
+                    xs = [rand(count, dtype, 10 * r + count % 7) for r in range(n)]
+                    outs = [torch.full_like(x, float("nan")) for x in xs]
+                    grp.run("allreduce", xs, outs, count, op=op, algo="NVLS")
+                    healthy(f"allreduce {dtype} {count} {op}")
+                    calls += 1
+                    want = reduce_ref(xs, op)
+                    for r in range(n):
+                        assert torch.allclose(outs[r].float(), want, atol=tol(dtype, n), rtol=1e-2), f"allreduce n={n} {dtype} {count} {op} rank {r}: {(outs[r].float() - want).abs().max().item()}"
+                        assert torch.equal(outs[r], outs[0]), "ranks differ"
+            # block collectives: blocks of a multiple of 16 bytes take the switch; interleaved so that half slots change hands
+            for count in (16 // es, (48 * 1024) // es, (24 * 1024 + 16) // es):
+                xs = [rand(count, dtype, 100 + r) for r in range(n)]
+                # all-gather
+                outs = [torch.full((n * count,), float("nan"), device="cuda", dtype=dtype) for _ in range(n)]
+                grp.run("allgather", xs, outs, count, algo="NVLS")
+                healthy("allgather")
+                calls += 1
+                want = torch.cat(xs)
+                for r in range(n):
+                    assert torch.equal(outs[r], want), f"allgather n={n} {dtype} {count} rank {r}"
+                # reduce-scatter
+                big = [rand(n * count, dtype, 200 + r) for r in range(n)]
+                rs = [torch.full((count,), float("nan"), device="cuda", dtype=dtype) for _ in range(n)]
+                grp.run("reduce_scatter", big, rs, count, op="sum", algo="NVLS")
+                healthy("reduce_scatter")
+                calls += 1
+                want = reduce_ref(big, "sum")
+                for r in range(n):
+                    assert torch.allclose(rs[r].float(), want[r * count:(r + 1) * count], atol=tol(dtype, n), rtol=1e-2), f"reduce_scatter n={n} {dtype} {count} rank {r}"
+                # broadcast from the last rank, in place
+                root = n - 1
+                bs = [x.clone() for x in xs]
+                grp.run("broadcast", bs, bs, count, root=root, algo="NVLS")
+                healthy("broadcast")
+                calls += 1
+                for r in range(n):
+                    assert torch.equal(bs[r], xs[root]), f"broadcast n={n} {dtype} {count} rank {r}"
+                # reduce to rank 1
+                outs = [torch.full_like(x, float("nan")) for x in xs]
+                op = "max" if dtype != torch.float32 else "sum"
+                grp.run("reduce", xs, outs, count, op=op, root=1, algo="NVLS")
+                healthy("reduce")
+                calls += 1
+                assert torch.allclose(outs[1].float(), reduce_ref(xs, op), atol=tol(dtype, n), rtol=1e-2), f"reduce n={n} {dtype} {count}"
+                assert torch.isnan(outs[0].float()).all(), "only the root's receive buffer is written"
+            # user buffers that start 2 or 4 bytes past a 16-byte boundary, and in-place all-gather / reduce-scatter
+            count = (40 * 1024) // es
+            bases = [rand(count * n + 1, dtype, 300 + r) for r in range(n)]
+            xs = [b[1:1 + count] for b in bases]
+            want = reduce_ref(xs, "sum")
+            grp.run("allreduce", xs, xs, count, op="sum", algo="NVLS")
+            healthy("allreduce unaligned in place")
+            calls += 1
+            for r in range(n):
+                assert torch.allclose(xs[r].float(), want, atol=tol(dtype, n), rtol=1e-2)
+            bases = [rand(count * n + 1, dtype, 400 + r) for r in range(n)]
+            bufs = [b[1:] for b in bases]
+            mine = [bufs[r][r * count:(r + 1) * count].clone() for r in range(n)]
+            grp.run("allgather", [bufs[r][r * count:(r + 1) * count] for r in range(n)], bufs, count, algo="NVLS")
+            healthy("allgather unaligned in place")
+            calls += 1
+            for r in range(n):
+                assert torch.equal(bufs[r], torch.cat(mine)), f"in-place all-gather rank {r}"
+            bases = [rand(count * n + 1, dtype, 500 + r) for r in range(n)]
+            bufs = [b[1:] for b in bases]
+            want = reduce_ref(bufs, "avg")
+            grp.run("reduce_scatter", bufs, [bufs[r][r * count:(r + 1) * count] for r in range(n)], count, op="avg", algo="NVLS")
+            healthy("reduce_scatter unaligned in place")
+            calls += 1
+            for r in range(n):
+                assert torch.allclose(bufs[r][r * count:(r + 1) * count].float(), want[r * count:(r + 1) * count], atol=tol(dtype, n), rtol=1e-2), f"in-place reduce-scatter rank {r}"
+        # every call above was eligible for the switch
+        assert grp.stats().nvls_calls - before == calls, (grp.stats().nvls_calls - before, calls)
+        expected_switch_calls += calls
+        # what the switch cannot reduce (fp32 max, integers) and blocks that are not a multiple of 16 bytes: the peer-to-peer schedules run
+        x32 = [rand(5000, torch.float32, 600 + r) for r in range(n)]
+        outs = [torch.empty_like(x) for x in x32]
+        grp.run("allreduce", x32, outs, 5000, op="max", algo="NVLS")
+        healthy("fp32 max")
+        assert torch.equal(outs[0], reduce_ref(x32, "max"))
+        xi = [torch.arange(999, device="cuda", dtype=torch.int32) * (r + 1) for r in range(n)]
+        outs = [torch.empty(n * 999, device="cuda", dtype=torch.int32) for _ in range(n)]
+        grp.run("allgather", xi, outs, 999, algo="NVLS")
+        healthy("int32 odd all-gather")
+        assert torch.equal(outs[n - 1], torch.cat(xi))
+        assert grp.stats().nvls_calls - before == calls
+        # AUTO picks the switch for large messages when a window exists
+        big = [rand(1 << 20, torch.bfloat16, 700 + r) for r in range(n)]
+        outs = [torch.empty_like(x) for x in big]
+        grp.run("allreduce", big, outs, 1 << 20, op="sum", algo="AUTO")
+        healthy("auto")
+        assert grp.stats().nvls_calls - before == calls + 1
+        assert torch.allclose(outs[0].float(), reduce_ref(big, "sum"), atol=tol(torch.bfloat16, n), rtol=1e-2)
+        grp.close()
+    print(f"NVLS_EMULATED_OK {expected_switch_calls} collectives through the emulated switch")
 
 
 if __name__ == "__main__":

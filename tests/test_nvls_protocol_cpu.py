@@ -1,13 +1,15 @@
-"""Exhaustive interleaving check of the barrier / slot protocol of the in-switch all-reduce kernels
-(src/kernels/nvls_allreduce.cu), on a small model: a few ranks, one CTA index, a few chunks, two calls in a row.
+"""Exhaustive interleaving check of the counter / half-slot protocol of the in-switch collectives
+(src/kernels/nvls_coll.cu, described in src/kernels/nvls.cuh), on a small model: a few ranks, one CTA index, a few chunks,
+several calls of different collectives in a row.
 
 Each rank runs the kernel's sequence of phases; the explorer tries every order in which ranks can advance and in which
 counter arrivals can reach each rank (an arrival is delivered to every rank separately, in any order).  Data is modelled
-as tags: a copy-in marks the rank's slot "in, chunk j", the in-switch phase of rank x requires "in, j" in portion x of
-EVERY rank's slot and marks it "sum, j" everywhere, a copy-out requires "sum, j" in all portions of the own slot.  A stale
-or overwritten slot therefore shows up as a violation, a lost wake-up as a deadlock.  The release ordering of the real
-kernel (data before the arrival) is what makes it legal to apply a phase's writes at once, before its arrival is issued.
-The reference has no counterpart."""
+as tags per (rank's copy, half slot, portion): a fill marks portions "in, chunk", the in-switch sum of an all-reduce
+requires "in" in its portion of EVERY copy and marks it "sum" everywhere, a copy-out or a load-reduce requires what it
+reads to be there and marks it "done".  Writing over anything that is not "done" is a violation, so a half slot that is
+refilled too early (by the same or by another collective) shows up, and a lost wake-up shows up as a deadlock.  The
+release ordering of the real kernel (data before the arrival) is what makes it legal to apply a phase's writes at once,
+before its arrival is issued.  The reference has no counterpart."""
 import sys
 from pathlib import Path
 
@@ -15,156 +17,203 @@ import pytest
 
 sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
 
-# counters: 0 = plain kernel; 1, 2 = A of half slot 0 / 1; 3, 4 = B of half slot 0 / 1
-N_COUNTERS = 5
+FILLED, REDUCED, CONSUMED = 0, 1, 2
+N_COUNTERS = 6          # counter index = half * 3 + kind
 
 
-def plain_program(n, m, base, call):
-    """nvls_allreduce_kernel: one slot, one counter, two barriers per chunk."""
-    ops, nbar = [], base
-    for j in range(m):
-        g = (call, j)
-        ops.append(("ci", g, (0, 1)))
-        nbar += 1
-        ops += [("arrive", 0), ("wait", 0, nbar * n)]
-        ops.append(("r", g, (0, 1)))
-        nbar += 1
-        ops += [("arrive", 0), ("wait", 0, nbar * n)]
-        ops.append(("co", g, (0, 1)))
-    return ops, nbar
+def ctr(half, kind):
+    return half * 3 + kind
 
 
-def pipe_program(n, m, base, call, broken=None):
-    """nvls_allreduce_pipe_kernel: two half slots, counters A0 A1 B0 B1.  `base` = uses of each half slot so far.
-    The window slot of a CTA index is modelled as two halves; the plain kernel uses both for every chunk."""
+def program(coll, n, r, m, used, call, root=0, broken=None):
+    """The phases of rank r for one call of `coll` with m chunks, exactly in the order of nvls_coll_kernel.
+    used = [fills of half 0, fills of half 1, reductions of half 0, reductions of half 1] so far; returns (ops, used')."""
+    bu, by = used[:2], used[2:]
     ops = []
-    if m > 0:
-        ops += [("ci", (call, 0), (0,)), ("arrive", 1)]
+    g = lambda j: (call, j)
+
+    def wait_consumed(j):
+        s = j & 1
+        target = n * (bu[s] + (j >> 1))
+        if target and broken != "no_wait_consumed":
+            ops.append(("wait", ctr(s, CONSUMED), target))
+
+    if coll == "allreduce":
+        def fill(j):
+            wait_consumed(j)
+            ops.append(("fill_own", g(j), j & 1))
+            ops.append(("arrive", ctr(j & 1, FILLED), 1))
+        if m > 0:
+            fill(0)
+        for j in range(m):
+            s = j & 1
+            if broken != "no_wait_filled":
+                ops.append(("wait", ctr(s, FILLED), n * (bu[s] + (j >> 1) + 1)))
+            ops.append(("reduce_all", g(j), s, r))
+            ops.append(("arrive", ctr(s, REDUCED), 1))
+            if j + 1 < m:
+                fill(j + 1)
+            if broken != "no_wait_reduced":
+                ops.append(("wait", ctr(s, REDUCED), n * (by[s] + (j >> 1) + 1)))
+            ops.append(("copy_out", g(j), s, "sum"))
+            ops.append(("arrive", ctr(s, CONSUMED), 1))
+        new = [bu[0] + (m + 1) // 2, bu[1] + m // 2, by[0] + (m + 1) // 2, by[1] + m // 2]
+        return ops, new
+    filler = (r == root) if coll == "broadcast" else True
+    consumer = (r == root) if coll == "reduce" else True
+    fill_inc = n if coll == "broadcast" else 1
+    cons_inc = n if coll == "reduce" else 1
+
+    def fill(j):
+        wait_consumed(j)
+        s = j & 1
+        if coll == "allgather":
+            ops.append(("fill_all", g(j), s, (r,)))
+        elif coll == "broadcast":
+            ops.append(("fill_all", g(j), s, tuple(range(n))))
+        else:
+            ops.append(("fill_own", g(j), s))
+        ops.append(("arrive", ctr(s, FILLED), fill_inc))
+
+    if m > 0 and filler:
+        fill(0)
     for j in range(m):
         s = j & 1
-        target = n * (base[s] + (j >> 1) + 1)
-        g = (call, j)
-        if broken != "no_wait_a":
-            ops.append(("wait", 1 + s, target))
-        ops += [("r", g, (s,)), ("arrive", 3 + s)]
-        nxt = [("ci", (call, j + 1), (s ^ 1,)), ("arrive", 1 + (s ^ 1))] if j + 1 < m else []
-        tail = [("wait", 3 + s, target), ("co", g, (s,))]
-        if broken == "copy_in_after_copy_out_only":          # would be correct but serial: used as a sanity variant
-            ops += tail + nxt
-        elif broken == "no_wait_b":
-            ops += nxt + [("co", g, (s,))]
-        else:
-            ops += nxt + tail
-    used = [base[0] + (m + 1) // 2, base[1] + m // 2]
-    return ops, used
+        if filler and j + 1 < m:
+            fill(j + 1)
+        if consumer:
+            if broken != "no_wait_filled":
+                ops.append(("wait", ctr(s, FILLED), n * (bu[s] + (j >> 1) + 1)))
+            if coll in ("allgather", "broadcast"):
+                ops.append(("copy_out", g(j), s, "in"))
+            elif coll == "reduce_scatter":
+                ops.append(("reduce_local", g(j), s, (r,)))
+            else:
+                ops.append(("reduce_local", g(j), s, tuple(range(n))))
+            ops.append(("arrive", ctr(s, CONSUMED), cons_inc))
+    return ops, [bu[0] + (m + 1) // 2, bu[1] + m // 2, by[0], by[1]]
 
 
-def explore(n, programs, limit=3_000_000):
-    """programs[r]: list of ops.  Returns the number of states visited; raises AssertionError naming the violation or the deadlock."""
-    # state: pcs, delivered[src][c][dst], tags[rank][half][portion]
+def sequence(n, calls, broken=None):
+    """calls: list of (collective, chunks, root).  Returns the per-rank programs of the whole sequence."""
+    progs = [[] for _ in range(n)]
+    used = [0, 0, 0, 0]
+    for ci, (coll, m, root) in enumerate(calls):
+        nxt = None
+        for r in range(n):
+            ops, nxt = program(coll, n, r, m, used, ci, root, broken)
+            progs[r] += ops
+        used = nxt
+    return progs, used
+
+
+def explore(n, programs, limit=4_000_000):
+    """Returns the number of states visited; raises AssertionError naming the violation or the deadlock."""
+    # arrivals issued by src on counter c, in program order, as (position in the program, increment)
+    arrivals = [[[(i, op[2]) for i, op in enumerate(programs[src]) if op[0] == "arrive" and op[1] == c] for c in range(N_COUNTERS)] for src in range(n)]
     start = (tuple([0] * n), tuple([0] * (n * N_COUNTERS * n)), tuple([None] * (n * 2 * n)))
     seen = {start}
     stack = [start]
-
-    def issued(pcs, src, c):
-        return sum(1 for op in programs[src][:pcs[src]] if op[0] == "arrive" and op[1] == c)
-
+    free = lambda tag: tag is None or tag[0] == "done"
     while stack:
         pcs, deliv, tags = stack.pop()
-        moved = False
         succ = []
-        # deliveries
         for src in range(n):
             for c in range(N_COUNTERS):
-                iss = issued(pcs, src, c)
+                issued = sum(1 for pos, _ in arrivals[src][c] if pos < pcs[src])
                 for dst in range(n):
                     i = (src * N_COUNTERS + c) * n + dst
-                    if deliv[i] < iss:
+                    if deliv[i] < issued:
                         d = list(deliv); d[i] += 1
                         succ.append((pcs, tuple(d), tags))
-        # rank steps
         for r in range(n):
             if pcs[r] >= len(programs[r]):
                 continue
             op = programs[r][pcs[r]]
             t = list(tags)
+            at = lambda q, h, p: (q * 2 + h) * n + p
             if op[0] == "wait":
-                have = sum(deliv[(src * N_COUNTERS + op[1]) * n + r] for src in range(n))
+                have = sum(sum(inc for _, inc in arrivals[src][op[1]][:deliv[(src * N_COUNTERS + op[1]) * n + r]]) for src in range(n))
                 if have < op[2]:
                     continue
-            elif op[0] == "ci":
-                _, g, halves = op
-                for h in halves:
-                    for p in range(n):
-                        old = t[(r * 2 + h) * n + p]
-                        # overwriting data that somebody still needs: contributions not yet summed, sums not yet copied out
-                        assert old is None or old[0] == "done", f"rank {r} copies chunk {g} into half {h} over {old}"
-                        t[(r * 2 + h) * n + p] = ("in", g)
-            elif op[0] == "r":
-                _, g, halves = op
-                for h in halves:
-                    for q in range(n):
-                        old = t[(q * 2 + h) * n + r]
-                        assert old == ("in", g), f"rank {r} sums chunk {g} but rank {q}'s half {h} holds {old}"
-                    for q in range(n):
-                        t[(q * 2 + h) * n + r] = ("sum", g)
-            elif op[0] == "co":
-                _, g, halves = op
-                for h in halves:
-                    for p in range(n):
-                        old = t[(r * 2 + h) * n + p]
-                        assert old == ("sum", g), f"rank {r} copies chunk {g} out of half {h} but portion {p} holds {old}"
-                        t[(r * 2 + h) * n + p] = ("done", g)
+            elif op[0] == "fill_own":
+                _, g, h = op
+                for p in range(n):
+                    assert free(t[at(r, h, p)]), f"rank {r} fills half {h} with {g} over {t[at(r, h, p)]}"
+                    t[at(r, h, p)] = ("in", g)
+            elif op[0] == "fill_all":
+                _, g, h, portions = op
+                for q in range(n):
+                    for p in portions:
+                        assert free(t[at(q, h, p)]), f"rank {r} stores {g} into portion {p} of rank {q}'s half {h} over {t[at(q, h, p)]}"
+                        t[at(q, h, p)] = ("in", g)
+            elif op[0] == "reduce_all":
+                _, g, h, p = op
+                for q in range(n):
+                    assert t[at(q, h, p)] == ("in", g), f"rank {r} sums {g} but rank {q}'s half {h} holds {t[at(q, h, p)]}"
+                for q in range(n):
+                    t[at(q, h, p)] = ("sum", g)
+            elif op[0] == "copy_out":
+                _, g, h, want = op
+                for p in range(n):
+                    assert t[at(r, h, p)] == (want, g), f"rank {r} copies {g} out of half {h} but portion {p} holds {t[at(r, h, p)]}"
+                    t[at(r, h, p)] = ("done", g)
+            elif op[0] == "reduce_local":
+                _, g, h, portions = op
+                for q in range(n):
+                    for p in portions:
+                        assert t[at(q, h, p)] == ("in", g), f"rank {r} load-reduces {g} but portion {p} of rank {q}'s half {h} holds {t[at(q, h, p)]}"
+                for q in range(n):
+                    for p in portions:
+                        t[at(q, h, p)] = ("done", g)
             p2 = list(pcs); p2[r] += 1
             succ.append((tuple(p2), deliv, tuple(t)))
+        if not succ:
+            assert all(pcs[r] == len(programs[r]) for r in range(n)), f"deadlock at {pcs}: {[programs[r][pcs[r]] for r in range(n) if pcs[r] < len(programs[r])]}"
         for s in succ:
-            moved = True
             if s not in seen:
                 seen.add(s)
                 stack.append(s)
                 assert len(seen) < limit, "state space larger than expected"
-        if not moved:
-            assert all(pcs[r] == len(programs[r]) for r in range(n)), f"deadlock at {pcs}: {[programs[r][pcs[r]] for r in range(n) if pcs[r] < len(programs[r])]}"
     return len(seen)
 
 
-def two_calls(n, kinds, m):
-    """Every rank runs two kernels in a row (kinds: 'plain' / 'pipe'), m chunks each."""
-    ops, nbar, used = [], 0, [0, 0]
-    for call, kind in enumerate(kinds):
-        if kind == "plain":
-            o, nbar = plain_program(n, m, nbar, call)
-        else:
-            o, used = pipe_program(n, m, used, call)
-        ops += o
-    return [list(ops) for _ in range(n)]
+@pytest.mark.parametrize("calls", [
+    [("allreduce", 3, 0), ("allreduce", 2, 0)],
+    [("allreduce", 2, 0), ("allgather", 3, 0)],
+    [("allgather", 3, 0), ("allreduce", 2, 0)],
+    [("reduce_scatter", 3, 0), ("allreduce", 2, 0)],
+    [("broadcast", 3, 1), ("reduce", 3, 0)],
+    [("reduce", 2, 1), ("allgather", 2, 0), ("broadcast", 2, 0)],
+    [("allreduce", 1, 0), ("reduce_scatter", 2, 0), ("allgather", 1, 0)],
+])
+def test_every_interleaving_of_two_ranks_is_safe_and_terminates(calls):
+    progs, _ = sequence(2, calls)
+    assert explore(2, progs) > 50
 
 
-@pytest.mark.parametrize("kinds,n,m", [(("plain", "plain"), 2, 2), (("pipe", "pipe"), 2, 3), (("pipe", "plain"), 2, 2), (("plain", "pipe"), 2, 3),
-                                       (("pipe",), 3, 2), (("plain",), 3, 2)])
-def test_every_interleaving_is_safe_and_terminates(kinds, n, m):
-    states = explore(n, two_calls(n, kinds, m))
-    assert states > 100
+@pytest.mark.parametrize("calls", [[("allreduce", 1, 0)], [("allgather", 1, 0)], [("reduce_scatter", 1, 0)], [("broadcast", 1, 2)], [("reduce", 1, 1)], [("broadcast", 1, 0), ("reduce", 1, 2)]])
+def test_three_ranks(calls):
+    progs, _ = sequence(3, calls)
+    explore(3, progs)
 
 
 def test_odd_and_even_chunk_counts_keep_the_half_slot_counters_in_step():
     # 3 chunks then 2 chunks: half slot 0 was used twice, half slot 1 once, before the second call
-    n = 2
-    o1, used = pipe_program(n, 3, [0, 0], 0)
-    o2, used2 = pipe_program(n, 2, used, 1)
-    assert used == [2, 1] and used2 == [3, 2]
-    explore(n, [o1 + o2 for _ in range(n)])
+    progs, used = sequence(2, [("allreduce", 3, 0), ("allgather", 2, 0)])
+    assert used == [3, 2, 2, 1]
+    explore(2, progs)
 
 
-@pytest.mark.parametrize("broken", ["no_wait_b", "no_wait_a"])
-def test_the_checker_finds_a_missing_wait(broken):
-    n, m = 2, 3
-    prog, _ = pipe_program(n, m, [0, 0], 0, broken=broken)
+@pytest.mark.parametrize("calls,broken", [
+    ([("allreduce", 3, 0)], "no_wait_filled"),
+    ([("allreduce", 3, 0)], "no_wait_reduced"),
+    ([("allgather", 3, 0)], "no_wait_consumed"),          # the third chunk is stored over the first before it was copied out
+    ([("allreduce", 1, 0), ("allgather", 1, 0)], "no_wait_consumed"),   # another collective takes the half slot over too early
+    ([("reduce_scatter", 3, 0)], "no_wait_consumed"),     # the own copy is refilled while a peer still load-reduces from it
+    ([("broadcast", 2, 0)], "no_wait_filled"),
+])
+def test_the_checker_finds_a_missing_wait(calls, broken):
+    progs, _ = sequence(2, calls, broken=broken)
     with pytest.raises(AssertionError):
-        explore(n, [list(prog) for _ in range(n)])
-
-
-def test_serial_order_is_also_safe():
-    n, m = 2, 3
-    prog, _ = pipe_program(n, m, [0, 0], 0, broken="copy_in_after_copy_out_only")
-    explore(n, [list(prog) for _ in range(n)])
+        explore(2, progs)

@@ -58,13 +58,13 @@ def test_protocol_switch_and_effective_configuration():
         return dict(kv.split("=", 1) for kv in out.split())
 
     d = describe()
-    assert d["proto"] == "auto" and d["ll_kb"] == "1024" and d["llf_kb"] == "64" and d["nvls"] == "0" and d["allreduce"] == "DEFAULT/-1"
+    assert d["proto"] == "auto" and d["ll_kb"] == "1024" and d["llf_kb"] == "64" and d["nvls"] == "1" and d["allreduce"] == "DEFAULT/-1"
     d = describe(PICCL_PROTO="simple")
     assert d["proto"] == "simple" and d["ll_kb"] == "0" and d["llf_kb"] == "0"
     d = describe(PICCL_PROTO="ll")
     assert d["proto"] == "ll" and d["llf_kb"] == "1024"
-    d = describe(PICCL_PROTO="nvls", PICCL_ALLREDUCE_ALGO="DIRECT", PICCL_ALLGATHER_ALGO="PRM", PICCL_ALLGATHER_K="4", PICCL_NVLS_PIPE="1")
-    assert d["proto"] == "nvls" and d["nvls"] == "1" and d["nvls_pipe"] == "1" and d["allreduce"] == "DIRECT/-1" and d["allgather"] == "PRM/4"
+    d = describe(PICCL_PROTO="nvls", PICCL_ALLREDUCE_ALGO="DIRECT", PICCL_ALLGATHER_ALGO="PRM", PICCL_ALLGATHER_K="4", PICCL_NVLS_MIN_KB="32")
+    assert d["proto"] == "nvls" and d["nvls"] == "1" and d["nvls_min_kb"] == "32" and d["allreduce"] == "DIRECT/-1" and d["allgather"] == "PRM/4"
     d = describe(PICCL_PROTO="bogus")
     assert d["proto"] == "auto"
 
