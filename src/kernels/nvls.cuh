@@ -8,21 +8,22 @@
 // Every rank owns a window of device memory that is bound, at the same offset,
 // to one multicast object, and sees it at two addresses: `uc` (its own copy)
 // and `mc` (all copies at once).  Layout of a window:
-//   [ kNvlsFlagBytes: counters, three per (CTA index, half slot), 128 bytes apart ]
-//   [ one slot of slot_bytes per CTA index, used as two half slots ]
+//   [ kNvlsFlagBytes: counters, three per (CTA index, part of its slot), 128 bytes apart ]
+//   [ one slot of slot_bytes per CTA index, used as `depth` parts ]
 // CTA b of every rank works on chunks b, b + n_cta, ... of the message; chunk j of a CTA goes
-// through half slot j & 1, so that the next chunk is staged while the current one is in the switch.
-// One use of a half slot has up to three stages, each closed by one counter that every rank
+// through part j % depth of its slot, and three groups of warps of the CTA (fill, switch, out) work
+// on different chunks at the same time.
+// One use of a part has up to three stages, each closed by one counter that every rank
 // raises (by n in total) on all copies with a single multimem.red:
-//   FILLED    the chunk is in the half slot   (all-reduce, reduce-scatter, reduce: every rank copied its own
+//   FILLED    the chunk is in the part            (all-reduce, reduce-scatter, reduce: every rank copied its own
 //             data into its own copy; all-gather: every rank stored its piece into every copy with
 //             multimem.st; broadcast: the root stored the chunk into every copy)
 //   REDUCED   all-reduce only: every rank has summed its 1/n of the chunk in the switch and stored the
 //             sums into every copy
-//   CONSUMED  nobody reads this use of the half slot any more (all-reduce, all-gather, broadcast: copied
+//   CONSUMED  nobody reads this use of the part any more (all-reduce, all-gather, broadcast: copied
 //             out; reduce-scatter / reduce: the multimem.ld_reduce that wrote the result straight to the
 //             receive buffer is done)
-// Nobody writes into a half slot before CONSUMED of its previous use is complete, whichever
+// Nobody writes into a part before CONSUMED of its previous use is complete, whichever
 // collective that use belonged to, so calls of different collectives may follow each other freely.
 // Counters only ever grow, over the life of the communicator; the number of uses so far is kept
 // in device memory, so a captured graph can be replayed.  Every poll is bounded: on a time-out
@@ -39,9 +40,10 @@
 namespace piccl {
 
 constexpr int kNvlsMaxCta = 128;
-constexpr int kNvlsFlagBytes = 131072;    // 128 CTA indices x 2 half slots x 3 counters x 128 bytes = 96 KiB, rounded up
+constexpr int kNvlsMaxDepth = 4;          // parts per slot, at most
+constexpr int kNvlsFlagBytes = 262144;    // 128 CTA indices x 4 parts x 3 counters x 128 bytes = 192 KiB, rounded up
 constexpr int kNvlsBlock = 512;
-constexpr int kNvlsUsedPerCta = 4;        // uses so far per CTA index: FILLED/CONSUMED of half slot 0, 1; REDUCED of half slot 0, 1
+constexpr int kNvlsUsedPerCta = 2 * kNvlsMaxDepth;   // uses so far per CTA index: fills of part 0..3, then reductions (all-reduce) of part 0..3
 enum NvlsCounter : int { NVC_FILLED = 0, NVC_REDUCED = 1, NVC_CONSUMED = 2 };
 
 struct NvlsRank {
@@ -51,7 +53,11 @@ struct NvlsRank {
   int* abort_flag;
   piccl_status_t* status;
   int rank, pad;
+  unsigned long long* prof;               // PICCL_NVLS_PROFILE=1: [kNvlsProfSlots] nanoseconds summed over CTAs and calls (null: off)
 };
+// profile slots: time of thread 0 inside each kind of phase, and chunks / CTAs counted
+enum NvlsProf : int { NVP_FILL = 0, NVP_WAIT_FILLED = 1, NVP_SWITCH = 2, NVP_WAIT_REDUCED = 3, NVP_OUT = 4, NVP_WAIT_CONSUMED = 5, NVP_CHUNKS = 6, NVP_CTAS = 7, NVP_TOTAL = 8 };
+constexpr int kNvlsProfSlots = 16;
 
 struct NvlsArgs {
   int coll, nranks, n_cta, n_vrank;
@@ -60,8 +66,9 @@ struct NvlsArgs {
   int pad;
   long long bytes;                        // all-reduce, broadcast, reduce: message bytes; all-gather, reduce-scatter: bytes of one rank's block
   long long chunk_bytes;                  // bytes of the message (or of each rank's block) per chunk; a multiple of 16, of 16 * nranks for all-reduce
-  long long sub_stride;                   // all-gather, reduce-scatter: distance between two ranks' pieces inside a half slot (>= chunk_bytes, multiple of 16)
-  long long slot_bytes;                   // distance between two slots; a half slot is slot_bytes / 2 (multiple of 16)
+  long long sub_stride;                   // all-gather, reduce-scatter: distance between two ranks' pieces inside a part (>= chunk_bytes, multiple of 16)
+  long long slot_bytes;                   // distance between two slots; a part is slot_bytes / depth (multiple of 16)
+  int depth, pad2;                        // parts per slot (2 .. kNvlsMaxDepth): chunks a CTA has in flight
   unsigned long long timeout_ns;
   NvlsRank r[kMaxVRanks];
 };

@@ -35,21 +35,36 @@ template <> __device__ __forceinline__ __half nv_down<__half>(float v) { return 
 template <> __device__ __forceinline__ __nv_bfloat16 nv_down<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <int OP> __device__ __forceinline__ float nv_red(float x, float y) { return OP == 0 ? x + y : OP == 2 ? (x > y ? x : y) : (x < y ? x : y); }
 
-// 16 bytes of a user buffer that need not be 16-byte aligned (it is aligned to its element type)
-template <typename T> __device__ __forceinline__ uint4 ld_user(const char* p, bool aligned) {
-  if (aligned) return nv_ld_plain(p);
+// A user buffer need not be 16-byte aligned, and for the collectives that only move data T is not the caller's element
+// type, so the buffer need not even be aligned to T.  Alignment class of an address: 2 = 16 bytes, 1 = T, 0 = bytes.
+template <typename T> __device__ __forceinline__ int align_class(const void* p) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  return (a & 15) == 0 ? 2 : (a & (sizeof(T) - 1)) == 0 ? 1 : 0;
+}
+template <typename T> __device__ __forceinline__ uint4 ld_user(const char* p, int al) {
+  if (al == 2) return nv_ld_plain(p);
   constexpr int N = 16 / sizeof(T);
-  union { uint4 v; T t[N]; } u;
+  union { uint4 v; T t[N]; unsigned char b[16]; } u;
+  if (al == 1) {
 #pragma unroll
-  for (int e = 0; e < N; e++) u.t[e] = reinterpret_cast<const T*>(p)[e];
+    for (int e = 0; e < N; e++) u.t[e] = reinterpret_cast<const T*>(p)[e];
+  } else {
+#pragma unroll
+    for (int e = 0; e < 16; e++) u.b[e] = reinterpret_cast<const unsigned char*>(p)[e];
+  }
   return u.v;
 }
-template <typename T> __device__ __forceinline__ void st_user(char* p, const uint4& v, bool aligned) {
-  if (aligned) { nv_st(p, v); return; }
+template <typename T> __device__ __forceinline__ void st_user(char* p, const uint4& v, int al) {
+  if (al == 2) { nv_st(p, v); return; }
   constexpr int N = 16 / sizeof(T);
-  union { uint4 v; T t[N]; } u; u.v = v;
+  union { uint4 v; T t[N]; unsigned char b[16]; } u; u.v = v;
+  if (al == 1) {
 #pragma unroll
-  for (int e = 0; e < N; e++) reinterpret_cast<T*>(p)[e] = u.t[e];
+    for (int e = 0; e < N; e++) reinterpret_cast<T*>(p)[e] = u.t[e];
+  } else {
+#pragma unroll
+    for (int e = 0; e < 16; e++) reinterpret_cast<unsigned char*>(p)[e] = u.b[e];
+  }
 }
 
 // ---------------------------------------------------------------- the switch
@@ -117,12 +132,17 @@ template <typename T, int OP, bool EMU> struct Switch {
 // nblk blocks of `len` bytes: block q from src + q * src_stride to dst + q * dst_stride.  With every address, stride and
 // length a multiple of 16 the blocks are moved as one flat sequence of 16-byte packs, U in flight per thread; otherwise
 // element by element.  `scale_on` multiplies by `scale` on the way (avg); src_volatile: the source was written by the switch.
+// One group of warps of a CTA that works on its own stage of the pipeline: thread index inside the group, threads of the
+// group, and the named barrier the group synchronises on.
+struct Role { int tid, nthr, bar; };
+__device__ __forceinline__ void role_sync(const Role& g) { asm volatile("bar.sync %0, %1;" ::"r"(g.bar), "r"(g.nthr) : "memory"); }
+
 template <typename T, int U>
-__device__ __forceinline__ void copy_blocks(char* dst, long long dst_stride, const char* src, long long src_stride, int nblk, long long len, bool src_volatile,
+__device__ __forceinline__ void copy_blocks(const Role& g, char* dst, long long dst_stride, const char* src, long long src_stride, int nblk, long long len, bool src_volatile,
                                             bool scale_on, float scale) {
   constexpr int N = 16 / sizeof(T);
   const bool fast = (((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src) | (uintptr_t)dst_stride | (uintptr_t)src_stride) & 15) == 0);
-  const int nt = blockDim.x;
+  const int nt = g.nthr, tid = g.tid;
   if (fast) {
     const int ppb = (int)(len >> 4);                    // whole packs per block
     const int total = ppb * nblk;
@@ -136,7 +156,7 @@ __device__ __forceinline__ void copy_blocks(char* dst, long long dst_stride, con
       return u.v;
     };
     const int done = (total / (nt * U)) * (nt * U);
-    for (int base = threadIdx.x; base < done; base += nt * U) {
+    for (int base = tid; base < done; base += nt * U) {
       uint4 v[U];
 #pragma unroll
       for (int u = 0; u < U; u++) { const char* sp = src_of(base + u * nt); v[u] = src_volatile ? nv_ld_volatile(sp) : nv_ld_plain(sp); }
@@ -147,7 +167,7 @@ __device__ __forceinline__ void copy_blocks(char* dst, long long dst_stride, con
 #pragma unroll
       for (int u = 0; u < U; u++) nv_st(dst_of(base + u * nt), v[u]);
     }
-    for (int p = done + threadIdx.x; p < total; p += nt) {
+    for (int p = done + tid; p < total; p += nt) {
       const char* sp = src_of(p);
       uint4 v = src_volatile ? nv_ld_volatile(sp) : nv_ld_plain(sp);
       if (scale_on) v = scaled(v);
@@ -157,90 +177,97 @@ __device__ __forceinline__ void copy_blocks(char* dst, long long dst_stride, con
     const int tail0 = ppb * N, nelem = (int)(len / (long long)sizeof(T));
     if (tail0 < nelem) {
       const int per = nelem - tail0;
-      for (int t = threadIdx.x; t < per * nblk; t += nt) {
+      for (int t = tid; t < per * nblk; t += nt) {
         const int q = t / per, i = tail0 + (t - q * per);
         T v = src_volatile ? reinterpret_cast<const volatile T*>(src + (long long)q * src_stride)[i] : reinterpret_cast<const T*>(src + (long long)q * src_stride)[i];
         reinterpret_cast<T*>(dst + (long long)q * dst_stride)[i] = scale_on ? nv_down<T>(nv_up<T>(v) * scale) : v;
       }
     }
-  } else {
+  } else if (((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & (sizeof(T) - 1)) == 0) {
     const long long nelem = len / (long long)sizeof(T);
     for (int q = 0; q < nblk; q++) {
       const T* s = reinterpret_cast<const T*>(src + (long long)q * src_stride); T* d = reinterpret_cast<T*>(dst + (long long)q * dst_stride);
-      for (long long i = threadIdx.x; i < nelem; i += nt) {
+      for (long long i = tid; i < nelem; i += nt) {
         T v = src_volatile ? reinterpret_cast<const volatile T*>(s)[i] : s[i];
         d[i] = scale_on ? nv_down<T>(nv_up<T>(v) * scale) : v;
       }
+    }
+  } else {
+    // not even aligned to T: only the collectives that move data get here (T is then not the caller's type), never with scaling
+    for (int q = 0; q < nblk; q++) {
+      const unsigned char* s = reinterpret_cast<const unsigned char*>(src + (long long)q * src_stride); unsigned char* d = reinterpret_cast<unsigned char*>(dst + (long long)q * dst_stride);
+      for (long long i = tid; i < len; i += nt) d[i] = src_volatile ? reinterpret_cast<const volatile unsigned char*>(s)[i] : s[i];
     }
   }
 }
 
 // `len` bytes (a multiple of 16) from the user buffer `src` to window offset `off` of every copy
 template <typename T, typename SW>
-__device__ __forceinline__ void store_all(const SW& sw, long long off, const char* src, long long len) {
+__device__ __forceinline__ void store_all(const SW& sw, const Role& g, long long off, const char* src, long long len) {
   constexpr int U = 8;
-  const bool al = (reinterpret_cast<uintptr_t>(src) & 15) == 0;
-  const int nt = blockDim.x, total = (int)(len >> 4);
+  const int al = align_class<T>(src);
+  const int nt = g.nthr, tid = g.tid, total = (int)(len >> 4);
   const int done = (total / (nt * U)) * (nt * U);
-  for (int base = threadIdx.x; base < done; base += nt * U) {
+  for (int base = tid; base < done; base += nt * U) {
     uint4 v[U];
 #pragma unroll
     for (int u = 0; u < U; u++) v[u] = ld_user<T>(src + ((long long)(base + u * nt) << 4), al);
 #pragma unroll
     for (int u = 0; u < U; u++) sw.st_all(off + ((long long)(base + u * nt) << 4), v[u]);
   }
-  for (int p = done + threadIdx.x; p < total; p += nt) sw.st_all(off + ((long long)p << 4), ld_user<T>(src + ((long long)p << 4), al));
+  for (int p = done + tid; p < total; p += nt) sw.st_all(off + ((long long)p << 4), ld_user<T>(src + ((long long)p << 4), al));
 }
 
-// packs [lo, hi) of the half slot at window offset `off`: reduced in the switch, the result to every copy
+// packs [lo, hi) of the part of a slot at window offset `off`: reduced in the switch, the result to every copy
 template <typename SW>
-__device__ __forceinline__ void reduce_to_all(const SW& sw, long long off, int lo, int hi) {
-  constexpr int U = 4;
-  const int nt = blockDim.x;
+__device__ __forceinline__ void reduce_to_all(const SW& sw, const Role& g, long long off, int lo, int hi) {
+  constexpr int U = 8;
+  const int nt = g.nthr, tid = g.tid;
   const int done = lo + ((hi - lo) / (nt * U)) * (nt * U);
-  for (int base = lo + threadIdx.x; base < done; base += nt * U) {
+  for (int base = lo + tid; base < done; base += nt * U) {
     uint4 v[U];
 #pragma unroll
     for (int u = 0; u < U; u++) v[u] = sw.ld_reduce(off + ((long long)(base + u * nt) << 4));
 #pragma unroll
     for (int u = 0; u < U; u++) sw.st_all(off + ((long long)(base + u * nt) << 4), v[u]);
   }
-  for (int p = done + threadIdx.x; p < hi; p += nt) { const long long o = off + ((long long)p << 4); sw.st_all(o, sw.ld_reduce(o)); }
+  for (int p = done + tid; p < hi; p += nt) { const long long o = off + ((long long)p << 4); sw.st_all(o, sw.ld_reduce(o)); }
 }
 
 // `len` bytes (a multiple of 16) at window offset `off`, reduced in the switch, to the user buffer `dst`
 template <typename T, typename SW>
-__device__ __forceinline__ void reduce_to_local(const SW& sw, long long off, char* dst, long long len) {
-  constexpr int U = 4;
-  const bool al = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
-  const int nt = blockDim.x, total = (int)(len >> 4);
+__device__ __forceinline__ void reduce_to_local(const SW& sw, const Role& g, long long off, char* dst, long long len) {
+  constexpr int U = 8;
+  const int al = align_class<T>(dst);
+  const int nt = g.nthr, tid = g.tid, total = (int)(len >> 4);
   const int done = (total / (nt * U)) * (nt * U);
-  for (int base = threadIdx.x; base < done; base += nt * U) {
+  for (int base = tid; base < done; base += nt * U) {
     uint4 v[U];
 #pragma unroll
     for (int u = 0; u < U; u++) v[u] = sw.ld_reduce(off + ((long long)(base + u * nt) << 4));
 #pragma unroll
     for (int u = 0; u < U; u++) st_user<T>(dst + ((long long)(base + u * nt) << 4), v[u], al);
   }
-  for (int p = done + threadIdx.x; p < total; p += nt) st_user<T>(dst + ((long long)p << 4), sw.ld_reduce(off + ((long long)p << 4)), al);
+  for (int p = done + tid; p < total; p += nt) st_user<T>(dst + ((long long)p << 4), sw.ld_reduce(off + ((long long)p << 4)), al);
 }
 
 // ---------------------------------------------------------------- counters
-// The CTA's accesses so far are ordered before `inc` more arrivals on every copy of the counter.
+// The group's accesses so far are ordered before `inc` more arrivals on every copy of the counter.
 template <typename SW>
-__device__ __forceinline__ void nv_arrive(const SW& sw, long long flag_off, unsigned long long inc) {
-  __syncthreads();
-  if (threadIdx.x == 0) {
+__device__ __forceinline__ void nv_arrive(const SW& sw, const Role& g, long long flag_off, unsigned long long inc) {
+  role_sync(g);
+  if (g.tid == 0) {
     __threadfence_system();
     sw.add_all(flag_off, inc);
   }
 }
 
-// Bounded wait of the whole CTA until the own copy of the counter shows `target`.  false: the wait ran out or the communicator was aborted.
-__device__ __forceinline__ bool nv_wait(const NvlsArgs& a, const NvlsRank& R, int cta, long long flag_off, unsigned long long target, int stage, long long chunk,
+// Bounded wait of the whole group until the own copy of the counter shows `target`.  false: the wait ran out or the communicator was aborted.
+// `s_fail` belongs to the group: only its thread 0 writes it, and all its threads read it after the group's barrier.
+__device__ __forceinline__ bool nv_wait(const NvlsArgs& a, const NvlsRank& R, const Role& g, int cta, long long flag_off, unsigned long long target, int stage, long long chunk,
                                         int* s_fail) {
-  if (target == 0) return true;                       // first use of the half slot: nothing to wait for (the same in every thread)
-  if (threadIdx.x == 0) {
+  if (target == 0) return true;                       // first use of this part of the slot: nothing to wait for (the same in every thread)
+  if (g.tid == 0) {
     const unsigned long long* flag = reinterpret_cast<const unsigned long long*>(R.uc + flag_off);
     unsigned long long t0 = 0, have = 0;
     bool ok = false, timed_out = false;
@@ -266,27 +293,32 @@ __device__ __forceinline__ bool nv_wait(const NvlsArgs& a, const NvlsRank& R, in
       *s_fail = 1;
     }
   }
-  __syncthreads();
+  role_sync(g);
   return *(volatile int*)s_fail == 0;
 }
 
 // ---------------------------------------------------------------- the kernel
+// Three groups of warps per CTA, each looping over the CTA's chunks on its own and meeting the others only through the
+// counters (which include this rank's own arrivals):
+//   FILL    waits until the part of the slot is free (CONSUMED of its previous use), stages the chunk, raises FILLED
+//   SWITCH  all-reduce only: waits for FILLED, sums its 1/n of the chunk in the switch and stores it to all copies, raises REDUCED
+//   OUT     waits for REDUCED (all-reduce) or FILLED, moves the result to the receive buffer, raises CONSUMED
+// With `depth` parts per slot the three stages of a CTA work on different chunks at the same time.
 template <typename T, int OP, bool EMU>
 __global__ void __launch_bounds__(kNvlsBlock, 1) nvls_coll_kernel(const __grid_constant__ NvlsArgs a) {
-  __shared__ int s_fail;
+  __shared__ int s_fail[3];
   const int vr = blockIdx.x / a.n_cta, cta = blockIdx.x - vr * a.n_cta;
   const NvlsRank& R = a.r[vr];
   const Switch<T, OP, EMU> sw(a, R);
-  if (threadIdx.x == 0) s_fail = 0;
+  if (threadIdx.x < 3) s_fail[threadIdx.x] = 0;
   __syncthreads();
-  const int n = a.nranks, rank = R.rank;
+  const int n = a.nranks, rank = R.rank, D = a.depth;
   const unsigned long long N = (unsigned long long)n;
   unsigned long long* const used = R.used + (long long)cta * kNvlsUsedPerCta;
-  const unsigned long long bu[2] = {used[0], used[1]}, by[2] = {used[2], used[3]};
-  const long long half_bytes = a.slot_bytes >> 1;
+  const long long part_bytes = a.slot_bytes / D;
   const long long slot0 = (long long)kNvlsFlagBytes + (long long)cta * a.slot_bytes;
-  auto slot = [&](int s) { return slot0 + (long long)s * half_bytes; };
-  auto flag = [&](int s, int which) { return (long long)(((cta * 2 + s) * 3 + which) * 128); };
+  auto part = [&](int p) { return slot0 + (long long)p * part_bytes; };
+  auto flag = [&](int p, int which) { return (long long)(((cta * kNvlsMaxDepth + p) * 3 + which) * 128); };
   const long long nchunks = (a.bytes + a.chunk_bytes - 1) / a.chunk_bytes;
   const long long m = cta < nchunks ? (nchunks - cta + a.n_cta - 1) / a.n_cta : 0;     // chunks of this CTA
   auto off_of = [&](long long j) { return (cta + j * a.n_cta) * a.chunk_bytes; };
@@ -294,91 +326,100 @@ __global__ void __launch_bounds__(kNvlsBlock, 1) nvls_coll_kernel(const __grid_c
   const char* const in = static_cast<const char*>(R.in);
   char* const out = static_cast<char*>(R.out);
   const bool scale_on = a.avg != 0;
-  bool ok = true;
+  const bool allreduce = a.coll == COLL_ALLREDUCE;
+  const bool filler = a.coll == COLL_BROADCAST ? rank == a.root : true;
+  const bool consumer = a.coll == COLL_REDUCE ? rank == a.root : true;
+  const unsigned long long fill_inc = a.coll == COLL_BROADCAST ? N : 1, cons_inc = a.coll == COLL_REDUCE ? N : 1;
 
-  if (a.coll == COLL_ALLREDUCE) {
-    auto fill = [&](long long j, int s) { copy_blocks<T, 8>(R.uc + slot(s), 0, in + off_of(j), 0, 1, len_of(j), false, scale_on, a.scale); };
-    if (m > 0) {
-      ok = nv_wait(a, R, cta, flag(0, NVC_CONSUMED), N * bu[0], NVC_CONSUMED, cta, &s_fail);
-      if (ok) { fill(0, 0); nv_arrive(sw, flag(0, NVC_FILLED), 1); }
+  // threads per group (multiples of 32): in proportion to the bytes each stage moves per chunk
+  int nF, nS = 0, nO;
+  switch (a.coll) {
+    case COLL_ALLREDUCE: if (n <= 2) { nF = 160; nS = 192; nO = 160; } else { nF = 192; nS = 128; nO = 192; } break;
+    case COLL_ALLGATHER: nF = n <= 2 ? 192 : 128; nO = kNvlsBlock - nF; break;
+    case COLL_REDUCE_SCATTER: nO = n <= 2 ? 192 : 128; nF = kNvlsBlock - nO; break;
+    case COLL_BROADCAST: if (!filler) { nF = 0; nO = kNvlsBlock; } else if (in == out) { nO = 32; nF = kNvlsBlock - 32; } else { nF = 256; nO = 256; } break;
+    default: if (!consumer) { nF = kNvlsBlock; nO = 0; } else { nF = 192; nO = 320; } break;      // reduce
+  }
+  const int t = threadIdx.x;
+  int role; Role g;
+  if (t < nF) { role = 0; g.tid = t; g.nthr = nF; g.bar = 1; }
+  else if (t < nF + nS) { role = 1; g.tid = t - nF; g.nthr = nS; g.bar = 2; }
+  else if (t < nF + nS + nO) { role = 2; g.tid = t - nF - nS; g.nthr = nO; g.bar = 3; }
+  else { role = -1; g.tid = 1; g.nthr = 32; g.bar = 4; }
+
+  // stopwatch of each group's thread 0 (PICCL_NVLS_PROFILE=1): the time since the last lap goes to one profile slot
+  const bool prof = R.prof != nullptr && role >= 0 && g.tid == 0 && m > 0;
+  unsigned long long t_last = prof ? nv_time_ns() : 0, t_first = t_last, acc[6] = {0, 0, 0, 0, 0, 0};
+  auto lap = [&](int slot_id) { if (prof) { const unsigned long long now = nv_time_ns(); acc[slot_id] += now - t_last; t_last = now; } };
+
+  if (role == 0 && filler) {
+    for (long long j = 0; j < m; j++) {
+      const int p = (int)(j % D);
+      const unsigned long long u = used[p] + (unsigned long long)(j / D);
+      const long long off = off_of(j), len = len_of(j);
+      // nobody reads the previous use of this part any more
+      if (!nv_wait(a, R, g, cta, flag(p, NVC_CONSUMED), N * u, NVC_CONSUMED, cta + j * a.n_cta, &s_fail[0])) break;
+      lap(NVP_WAIT_CONSUMED);
+      switch (a.coll) {
+        case COLL_ALLGATHER: store_all<T>(sw, g, part(p) + (long long)rank * a.sub_stride, in + off, len); break;
+        case COLL_BROADCAST: store_all<T>(sw, g, part(p), in + off, len); break;
+        case COLL_REDUCE_SCATTER: copy_blocks<T, 8>(g, R.uc + part(p), a.sub_stride, in + off, a.bytes, n, len, false, scale_on, a.scale); break;
+        default: copy_blocks<T, 8>(g, R.uc + part(p), 0, in + off, 0, 1, len, false, scale_on, a.scale); break;      // all-reduce, reduce
+      }
+      nv_arrive(sw, g, flag(p, NVC_FILLED), fill_inc);
+      lap(NVP_FILL);
     }
-    for (long long j = 0; j < m && ok; j++) {
-      const int s = (int)(j & 1);
-      const unsigned long long u = bu[s] + (unsigned long long)(j >> 1), uy = by[s] + (unsigned long long)(j >> 1);
-      const long long chunk = cta + j * a.n_cta, len = len_of(j);
+  } else if (role == 1 && allreduce) {
+    for (long long j = 0; j < m; j++) {
+      const int p = (int)(j % D);
+      const unsigned long long u = used[p] + (unsigned long long)(j / D);
+      const long long len = len_of(j);
       // every rank has copied chunk j in
-      ok = nv_wait(a, R, cta, flag(s, NVC_FILLED), N * (u + 1), NVC_FILLED, chunk, &s_fail);
-      if (!ok) break;
-      {
-        const int npack = (int)((len + 15) >> 4);          // the bytes past `len` in the last pack are summed too and never copied out
-        const int per = (npack + n - 1) / n;
-        int lo = rank * per; if (lo > npack) lo = npack;
-        int hi = lo + per; if (hi > npack) hi = npack;
-        reduce_to_all(sw, slot(s), lo, hi);
-      }
-      nv_arrive(sw, flag(s, NVC_REDUCED), 1);
-      // stage the next chunk while the other ranks finish their share of this one
-      if (j + 1 < m) {
-        const int s1 = s ^ 1;
-        ok = nv_wait(a, R, cta, flag(s1, NVC_CONSUMED), N * (bu[s1] + (unsigned long long)((j + 1) >> 1)), NVC_CONSUMED, chunk + a.n_cta, &s_fail);
-        if (!ok) break;
-        fill(j + 1, s1);
-        nv_arrive(sw, flag(s1, NVC_FILLED), 1);
-      }
-      // every rank has written its share of the sums of chunk j
-      ok = nv_wait(a, R, cta, flag(s, NVC_REDUCED), N * (uy + 1), NVC_REDUCED, chunk, &s_fail);
-      if (!ok) break;
-      copy_blocks<T, 8>(out + off_of(j), 0, R.uc + slot(s), 0, 1, len, true, false, 1.0f);
-      nv_arrive(sw, flag(s, NVC_CONSUMED), 1);
+      if (!nv_wait(a, R, g, cta, flag(p, NVC_FILLED), N * (u + 1), NVC_FILLED, cta + j * a.n_cta, &s_fail[1])) break;
+      lap(NVP_WAIT_FILLED);
+      const int npack = (int)((len + 15) >> 4);          // the bytes past `len` in the last pack are summed too and never copied out
+      const int per = (npack + n - 1) / n;
+      int lo = rank * per; if (lo > npack) lo = npack;
+      int hi = lo + per; if (hi > npack) hi = npack;
+      reduce_to_all(sw, g, part(p), lo, hi);
+      nv_arrive(sw, g, flag(p, NVC_REDUCED), 1);
+      lap(NVP_SWITCH);
     }
-  } else {
-    const bool filler = a.coll == COLL_BROADCAST ? rank == a.root : true;
-    const bool consumer = a.coll == COLL_REDUCE ? rank == a.root : true;
-    const unsigned long long fill_inc = a.coll == COLL_BROADCAST ? N : 1, cons_inc = a.coll == COLL_REDUCE ? N : 1;
-    auto fill = [&](long long j, int s) {
+  } else if (role == 2 && consumer) {
+    for (long long j = 0; j < m; j++) {
+      const int p = (int)(j % D);
+      const unsigned long long u = used[p] + (unsigned long long)(j / D), uy = used[kNvlsMaxDepth + p] + (unsigned long long)(j / D);
       const long long off = off_of(j), len = len_of(j);
+      if (allreduce) {
+        // every rank has written its share of the sums of chunk j
+        if (!nv_wait(a, R, g, cta, flag(p, NVC_REDUCED), N * (uy + 1), NVC_REDUCED, cta + j * a.n_cta, &s_fail[2])) break;
+        lap(NVP_WAIT_REDUCED);
+      } else {
+        if (!nv_wait(a, R, g, cta, flag(p, NVC_FILLED), N * (u + 1), NVC_FILLED, cta + j * a.n_cta, &s_fail[2])) break;
+        lap(NVP_WAIT_FILLED);
+      }
       switch (a.coll) {
-        case COLL_ALLGATHER: store_all<T>(sw, slot(s) + (long long)rank * a.sub_stride, in + off, len); break;
-        case COLL_BROADCAST: store_all<T>(sw, slot(s), in + off, len); break;
-        case COLL_REDUCE_SCATTER: copy_blocks<T, 8>(R.uc + slot(s), a.sub_stride, in + off, a.bytes, n, len, false, scale_on, a.scale); break;
-        default: copy_blocks<T, 8>(R.uc + slot(s), 0, in + off, 0, 1, len, false, scale_on, a.scale); break;      // reduce
+        case COLL_ALLGATHER: copy_blocks<T, 8>(g, out + off, a.bytes, R.uc + part(p), a.sub_stride, n, len, true, false, 1.0f); break;
+        case COLL_BROADCAST: if (!(rank == a.root && in == out)) copy_blocks<T, 8>(g, out + off, 0, R.uc + part(p), 0, 1, len, true, false, 1.0f); break;
+        case COLL_REDUCE_SCATTER: reduce_to_local<T>(sw, g, part(p) + (long long)rank * a.sub_stride, out + off, len); break;
+        case COLL_REDUCE: reduce_to_local<T>(sw, g, part(p), out + off, len); break;
+        default: copy_blocks<T, 8>(g, out + off, 0, R.uc + part(p), 0, 1, len, true, false, 1.0f); break;        // all-reduce
       }
-    };
-    auto consume = [&](long long j, int s) {
-      const long long off = off_of(j), len = len_of(j);
-      switch (a.coll) {
-        case COLL_ALLGATHER: copy_blocks<T, 8>(out + off, a.bytes, R.uc + slot(s), a.sub_stride, n, len, true, false, 1.0f); break;
-        case COLL_BROADCAST: if (!(rank == a.root && in == out)) copy_blocks<T, 8>(out + off, 0, R.uc + slot(s), 0, 1, len, true, false, 1.0f); break;
-        case COLL_REDUCE_SCATTER: reduce_to_local<T>(sw, slot(s) + (long long)rank * a.sub_stride, out + off, len); break;
-        default: reduce_to_local<T>(sw, slot(s), out + off, len); break;                                               // reduce, on the root
-      }
-    };
-    if (m > 0 && filler) {
-      ok = nv_wait(a, R, cta, flag(0, NVC_CONSUMED), N * bu[0], NVC_CONSUMED, cta, &s_fail);
-      if (ok) { fill(0, 0); nv_arrive(sw, flag(0, NVC_FILLED), fill_inc); }
-    }
-    for (long long j = 0; j < m && ok; j++) {
-      const int s = (int)(j & 1);
-      const unsigned long long u = bu[s] + (unsigned long long)(j >> 1);
-      const long long chunk = cta + j * a.n_cta;
-      if (filler && j + 1 < m) {
-        const int s1 = s ^ 1;
-        ok = nv_wait(a, R, cta, flag(s1, NVC_CONSUMED), N * (bu[s1] + (unsigned long long)((j + 1) >> 1)), NVC_CONSUMED, chunk + a.n_cta, &s_fail);
-        if (!ok) break;
-        fill(j + 1, s1);
-        nv_arrive(sw, flag(s1, NVC_FILLED), fill_inc);
-      }
-      if (consumer) {
-        ok = nv_wait(a, R, cta, flag(s, NVC_FILLED), N * (u + 1), NVC_FILLED, chunk, &s_fail);
-        if (!ok) break;
-        consume(j, s);
-        nv_arrive(sw, flag(s, NVC_CONSUMED), cons_inc);
-      }
+      nv_arrive(sw, g, flag(p, NVC_CONSUMED), cons_inc);
+      lap(NVP_OUT);
     }
   }
-  if (threadIdx.x == 0 && ok && m > 0) {
-    used[0] = bu[0] + (unsigned long long)((m + 1) / 2); used[1] = bu[1] + (unsigned long long)(m / 2);
-    if (a.coll == COLL_ALLREDUCE) { used[2] = by[0] + (unsigned long long)((m + 1) / 2); used[3] = by[1] + (unsigned long long)(m / 2); }
+  if (prof) {
+    for (int i = 0; i < 6; i++) if (acc[i]) atomicAdd(R.prof + i, acc[i]);
+    if (role == 2 || (role == 0 && !consumer)) { atomicAdd(R.prof + NVP_CHUNKS, (unsigned long long)m); atomicAdd(R.prof + NVP_CTAS, 1ull); atomicAdd(R.prof + NVP_TOTAL, nv_time_ns() - t_first); }
+  }
+  __syncthreads();                                    // every group is done with `used`
+  if (threadIdx.x == 0 && m > 0 && !(s_fail[0] | s_fail[1] | s_fail[2])) {
+    for (int p = 0; p < D; p++) {
+      const unsigned long long cnt = (unsigned long long)((m + D - 1 - p) / D);      // chunks j < m with j % D == p
+      used[p] += cnt;
+      if (allreduce) used[kNvlsMaxDepth + p] += cnt;
+    }
   }
 }
 

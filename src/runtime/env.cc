@@ -43,11 +43,13 @@ static void load() {
   e.tp_feeders = env_int("PICCL_TP_FEEDERS", 24); // CTAs that push the local shard in all-gather -> GEMM
   e.exec_defer = env_int("PICCL_EXEC_DEFER", 0);
   e.nvls = env_int("PICCL_NVLS", 1);            // 0: no NVLink multicast window (algorithm NVLS then runs the peer-to-peer schedules)
-  e.nvls_chunk_kb = env_int("PICCL_NVLS_CHUNK_KB", 256);   // half slot = largest chunk one CTA has in the switch at a time
-  e.nvls_cta = env_int("PICCL_NVLS_CTA", 64);              // CTAs (= slots of the window) of an in-switch collective
+  e.nvls_chunk_kb = env_int("PICCL_NVLS_CHUNK_KB", 128);   // largest chunk = one part of a CTA's slot
+  e.nvls_depth = env_int("PICCL_NVLS_DEPTH", 4);           // parts per slot (2 .. 4): chunks a CTA has in flight in its three stages
+  e.nvls_cta = env_int("PICCL_NVLS_CTA", 128);             // CTAs (= slots of the window) of an in-switch collective
   e.nvls_auto_kb = env_int("PICCL_NVLS_AUTO_KB", 256);     // AUTO sends messages above this size through the switch when a window exists
   e.nvls_min_kb = env_int("PICCL_NVLS_MIN_KB", 64);        // a mid-size message is cut into chunks of at least this size before more CTAs are used
-  { const char* g = getenv("PICCL_NVLS_GRAN"); e.nvls_gran_min = g && !strcmp(g, "min"); }
+  { const char* g = getenv("PICCL_NVLS_GRAN"); e.nvls_gran_min = !(g && !strcmp(g, "recommended")); }
+  e.nvls_profile = env_int("PICCL_NVLS_PROFILE", 0);       // 1: the kernels sum the time of every phase; printed when the communicator is destroyed
   // PICCL_PROTO narrows the choice of data path that is otherwise made per call by message size:
   //   auto    (default) low-latency kernels for small messages, the FIFO executor otherwise
   //   simple  FIFO executor only

@@ -19,6 +19,7 @@
 #include <fcntl.h>
 #include <unistd.h>
 #include <algorithm>
+#include <cstdio>
 #include <cstring>
 #include "comm.h"
 #include "fdshare.h"
@@ -80,7 +81,9 @@ struct NvlsState {
   CUdeviceptr uc_va = 0, mc_va = 0;
   size_t win = 0;
   long long slot_bytes = 0; int max_cta = 0;
-  unsigned long long* d_used = nullptr;      // uses of every half slot so far (kernels/nvls.cuh)
+  unsigned long long* d_used = nullptr;      // uses of every part of every slot so far (kernels/nvls.cuh)
+  int depth = 2;                             // parts per slot
+  unsigned long long* d_prof = nullptr;      // PICCL_NVLS_PROFILE=1: phase times summed by the kernels
   bool emulated = false; char* emu_win = nullptr;
 };
 
@@ -94,6 +97,7 @@ void teardown(NvlsState* s) {
   if (s->have_mem) { d.MemRelease(s->mem); s->have_mem = false; }
   if (s->have_mc) { d.MemRelease(s->mc); s->have_mc = false; }
   if (s->d_used) { cudaFree(s->d_used); s->d_used = nullptr; }
+  if (s->d_prof) { cudaFree(s->d_prof); s->d_prof = nullptr; }
   if (s->emu_win) { cudaFree(s->emu_win); s->emu_win = nullptr; }
   s->ready = false;
 }
@@ -130,8 +134,9 @@ bool nvls_emulated(const piccl_comm* c) { return nvls_ready(c) && static_cast<co
 static void window_geometry(NvlsState* s, bool emulated) {
   const Env& e = env();
   s->max_cta = std::max(1, std::min(e.nvls_cta, emulated ? 32 : kNvlsMaxCta));
-  s->slot_bytes = 2 * std::max<long long>(1, e.nvls_chunk_kb) * 1024;     // two half slots of PICCL_NVLS_CHUNK_KB
-  s->slot_bytes = (s->slot_bytes + 4095) / 4096 * 4096;
+  s->depth = std::max(2, std::min(e.nvls_depth, kNvlsMaxDepth));
+  const long long part = (std::max<long long>(1, e.nvls_chunk_kb) * 1024 + 255) / 256 * 256;     // one part = one chunk of at most PICCL_NVLS_CHUNK_KB
+  s->slot_bytes = s->depth * part;
 }
 
 // All ranks are virtual ranks of this process on this device: plain memory, the kernels loop over the ranks' windows.
@@ -151,7 +156,7 @@ void nvls_setup_emulated(piccl_comm* c) {
   s->ready = true;
 }
 
-// Before the window goes away: arrivals of the peers for this rank's last uses of each half slot may still be on their
+// Before the window goes away: arrivals of the peers for this rank's last uses of each part of a slot may still be on their
 // way (they are the last thing a peer's kernel does).  Waits on the host, with a limit, until every CONSUMED counter shows
 // all ranks; nothing writes into the window after that.
 static void quiesce(piccl_comm* c, NvlsState* s) {
@@ -163,9 +168,9 @@ static void quiesce(piccl_comm* c, NvlsState* s) {
     if (cudaMemcpy(flags.data(), (const void*)s->uc_va, kNvlsFlagBytes, cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return; }
     bool done = true;
     for (int b = 0; b < kNvlsMaxCta && done; b++)
-      for (int h = 0; h < 2; h++) {
+      for (int h = 0; h < kNvlsMaxDepth; h++) {
         const unsigned long long want = used[(size_t)b * kNvlsUsedPerCta + h] * (unsigned long long)c->nranks;
-        const unsigned long long have = flags[(size_t)(((b * 2 + h) * 3 + NVC_CONSUMED) * 128) / sizeof(unsigned long long)];
+        const unsigned long long have = flags[(size_t)(((b * kNvlsMaxDepth + h) * 3 + NVC_CONSUMED) * 128) / sizeof(unsigned long long)];
         if (have < want) { done = false; break; }
       }
     if (done) return;
@@ -177,6 +182,16 @@ static void quiesce(piccl_comm* c, NvlsState* s) {
 void nvls_destroy(piccl_comm* c) {
   if (!c->nvls) return;
   NvlsState* s = static_cast<NvlsState*>(c->nvls);
+  if (s->d_prof) {
+    // where thread 0 of the CTAs spent its time, per chunk, averaged over every CTA of every in-switch call of this communicator
+    unsigned long long h[kNvlsProfSlots] = {0};
+    if (cudaMemcpy(h, s->d_prof, sizeof h, cudaMemcpyDeviceToHost) == cudaSuccess && h[NVP_CHUNKS]) {
+      const double ch = (double)h[NVP_CHUNKS];
+      fprintf(stderr, "[PICCL %d] rank %d in-switch profile: %llu CTAs, %llu chunks; per chunk us: fill %.1f wait-filled %.1f switch %.1f wait-reduced %.1f out %.1f wait-consumed %.1f; per CTA us: %.1f\n",
+              (int)getpid(), c->rank, h[NVP_CTAS], h[NVP_CHUNKS], h[NVP_FILL] / ch / 1e3, h[NVP_WAIT_FILLED] / ch / 1e3, h[NVP_SWITCH] / ch / 1e3, h[NVP_WAIT_REDUCED] / ch / 1e3,
+              h[NVP_OUT] / ch / 1e3, h[NVP_WAIT_CONSUMED] / ch / 1e3, h[NVP_TOTAL] / (double)h[NVP_CTAS] / 1e3);
+    } else cudaGetLastError();
+  }
   quiesce(c, s);
   teardown(s);
   delete s;
@@ -205,7 +220,8 @@ void nvls_setup(piccl_comm* c, int root_pid, unsigned long long root_id) {
   ap.type = CU_MEM_ALLOCATION_TYPE_PINNED; ap.location.type = CU_MEM_LOCATION_TYPE_DEVICE; ap.location.id = c->device;
   ap.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
   size_t g_mc = 0, g_mem = 0;
-  // PICCL_NVLS_GRAN=min: the smallest granularity the driver accepts instead of the recommended one (512 MiB per window on B200)
+  // the smallest granularity the driver accepts (a 66 MiB window with the defaults on B200); PICCL_NVLS_GRAN=recommended: the
+  // recommended one, which makes every window 512 MiB
   const bool gran_min = e.nvls_gran_min != 0;
   STEP(d.MulticastGetGranularity(&g_mc, &mp, gran_min ? CU_MULTICAST_GRANULARITY_MINIMUM : CU_MULTICAST_GRANULARITY_RECOMMENDED));
   STEP(d.MemGetAllocationGranularity(&g_mem, &ap, gran_min ? CU_MEM_ALLOC_GRANULARITY_MINIMUM : CU_MEM_ALLOC_GRANULARITY_RECOMMENDED));
@@ -272,7 +288,7 @@ void nvls_setup(piccl_comm* c, int root_pid, unsigned long long root_id) {
     return;
   }
   s->ready = true;
-  log_msg(1, "rank %d: multicast window of %.1f MiB (%d slots of %lld KiB)", c->rank, s->win / 1048576.0, s->max_cta, s->slot_bytes >> 10);
+  log_msg(1, "rank %d: multicast window of %.1f MiB (%d slots of %d x %lld KiB)", c->rank, s->win / 1048576.0, s->max_cta, s->depth, (s->slot_bytes / s->depth) >> 10);
 }
 
 // What the kernels take: sum of fp32, sum / max / min of fp16 and bf16 (what the switch can reduce), any type for the
@@ -299,14 +315,14 @@ int nvls_collective(piccl_comm** comms, int n, int coll, const void* const* in, 
   const bool emu = s0->emulated;
   if (emu ? n != c0->nranks : n != 1) return PICCL_UNSUPPORTED;
   const int nr = c0->nranks;
-  const long long es = dtype_size(dtype), bytes = (long long)count * es, half = s0->slot_bytes / 2;
+  const long long es = dtype_size(dtype), bytes = (long long)count * es, half = s0->slot_bytes / s0->depth;
   const bool blocks = coll == COLL_ALLGATHER || coll == COLL_REDUCE_SCATTER;      // the message is one block per rank
   const bool reducing = coll == COLL_ALLREDUCE || coll == COLL_REDUCE || coll == COLL_REDUCE_SCATTER;
   NvlsArgs a; memset(&a, 0, sizeof a);
   a.coll = coll; a.nranks = nr; a.n_vrank = n; a.avg = (avg && reducing) ? 1 : 0; a.root = root; a.scale = a.avg ? 1.0f / (float)nr : 1.0f;
-  a.bytes = bytes; a.slot_bytes = s0->slot_bytes;
+  a.bytes = bytes; a.slot_bytes = s0->slot_bytes; a.depth = s0->depth;
   a.timeout_ns = (unsigned long long)c0->cfg.timeout_ms * 1000000ull;
-  // chunks: spread a mid-size message over all CTAs (at least PICCL_NVLS_MIN_KB of traffic per chunk), fill the half slots for a large one
+  // chunks: spread a mid-size message over all CTAs (at least PICCL_NVLS_MIN_KB of traffic per chunk), fill the parts of the slots for a large one
   const long long unit = coll == COLL_ALLREDUCE ? 16LL * nr : 16;
   const long long room = blocks ? (half / nr) / 16 * 16 : half / unit * unit;       // largest chunk (per rank block for all-gather / reduce-scatter)
   if (room < unit) return PICCL_UNSUPPORTED;
@@ -324,8 +340,13 @@ int nvls_collective(piccl_comm** comms, int n, int coll, const void* const* in, 
   for (int i = 0; i < n; i++) {
     piccl_comm* c = comms[i];
     NvlsState* s = static_cast<NvlsState*>(c->nvls);
-    if (!s || !s->ready || s->emulated != emu || s->slot_bytes != s0->slot_bytes) return PICCL_UNSUPPORTED;
+    if (!s || !s->ready || s->emulated != emu || s->slot_bytes != s0->slot_bytes || s->depth != s0->depth) return PICCL_UNSUPPORTED;
     NvlsRank& r = a.r[i];
+    if (env().nvls_profile && !s->d_prof) {
+      if (cudaMalloc(&s->d_prof, kNvlsProfSlots * sizeof(unsigned long long)) == cudaSuccess) cudaMemset(s->d_prof, 0, kNvlsProfSlots * sizeof(unsigned long long));
+      else { cudaGetLastError(); s->d_prof = nullptr; }
+    }
+    r.prof = s->d_prof;
     r.uc = (char*)s->uc_va; r.mc = (char*)s->mc_va; r.in = in[i]; r.out = out[i]; r.used = s->d_used; r.abort_flag = c->d_abort; r.status = c->d_status; r.rank = c->rank;
   }
   // copy-only collectives run any instantiation

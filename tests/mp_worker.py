@@ -222,33 +222,91 @@ def case_tp(rank, world):
 
 
 def case_nvls(rank, world):
-    """All-reduce summed inside the NVSwitch (PICCL_NVLS=1, algorithm NVLS) against NCCL."""
+    """Every collective through the NVSwitch (algorithm NVLS: multimem load-reduce, multicast stores) against NCCL."""
     from piccl_b200.parallel.comm import Communicator, make_config
     comm = Communicator(config=make_config(timeout_ms=20000))
     probe = torch.ones(1024, device="cuda")
     comm.all_reduce(probe, algo="NVLS")
     torch.cuda.synchronize()
     if comm.stats().nvls_calls == 0:
-        assert torch.equal(probe, torch.full_like(probe, float(world)))      # the ring ran instead
+        assert torch.equal(probe, torch.full_like(probe, float(world)))      # a peer-to-peer schedule ran instead
         print("NVLS_UNAVAILABLE", flush=True)
     else:
+        calls = 1
         for dtype, count in [(torch.float32, 1), (torch.float32, 1000), (torch.bfloat16, (1 << 20) + 3), (torch.float16, 300001), (torch.float32, 48 << 20)]:
-            for op in ("sum", "avg"):
+            for op in ("sum", "avg") if dtype == torch.float32 else ("sum", "avg", "max"):
                 x = rand(count, dtype, 300 + rank)
                 want = x.clone()
-                dist.all_reduce(want, op=dist.ReduceOp.AVG if op == "avg" else dist.ReduceOp.SUM)
+                dist.all_reduce(want, op={"sum": dist.ReduceOp.SUM, "avg": dist.ReduceOp.AVG, "max": dist.ReduceOp.MAX}[op])
                 got = comm.all_reduce(x.clone(), op=op, algo="NVLS")
+                calls += 1
                 healthy(comm)
                 assert torch.allclose(got.float(), want.float(), atol=tol(dtype, world), rtol=1e-2), f"nvls {op} {dtype} {count}: {(got.float() - want.float()).abs().max().item()}"
         # every rank ends with the same bits
         x = rand(1 << 20, torch.bfloat16, 400 + rank)
         got = comm.all_reduce(x, algo="NVLS")
+        calls += 1
         ref = got.clone()
         dist.broadcast(ref, 0)
         assert torch.equal(got, ref)
+        # the other collectives, interleaved; blocks of 16 bytes, of 1 MiB + 16 bytes and of 24 MiB
+        for dtype, count in [(torch.float32, 4), (torch.bfloat16, (1 << 19) + 8), (torch.float32, 6 << 20)]:
+            x = rand(count, dtype, 500 + rank)
+            out = torch.empty(world * count, dtype=dtype, device="cuda")
+            ref = torch.empty_like(out)
+            dist.all_gather_into_tensor(ref, x)
+            comm.all_gather(x, out, algo="NVLS")
+            healthy(comm)
+            assert torch.equal(out, ref), f"nvls allgather {dtype} {count}"
+            big = rand(world * count, dtype, 600 + rank)
+            rs_ref = torch.empty(count, dtype=dtype, device="cuda")
+            dist.reduce_scatter_tensor(rs_ref, big.clone())
+            rs = torch.empty(count, dtype=dtype, device="cuda")
+            comm.reduce_scatter(big, rs, algo="NVLS")
+            healthy(comm)
+            assert torch.allclose(rs.float(), rs_ref.float(), atol=tol(dtype, world), rtol=1e-2), f"nvls reduce_scatter {dtype} {count}"
+            root = world - 1
+            b = x.clone()
+            bref = x.clone()
+            dist.broadcast(bref, src=root)
+            comm.broadcast(b, root=root, algo="NVLS")
+            healthy(comm)
+            assert torch.equal(b, bref), f"nvls broadcast {dtype} {count}"
+            r_ref = x.clone()
+            dist.reduce(r_ref, dst=root)
+            r_out = torch.zeros_like(x)
+            comm.reduce(x, r_out, root=root, algo="NVLS")
+            healthy(comm)
+            if rank == root:
+                assert torch.allclose(r_out.float(), r_ref.float(), atol=tol(dtype, world), rtol=1e-2), f"nvls reduce {dtype} {count}"
+            calls += 4
+        assert comm.stats().nvls_calls == calls, (comm.stats().nvls_calls, calls)
+        # AUTO takes the switch for large messages
+        x = rand(8 << 20, torch.bfloat16, 700 + rank)
+        want = x.clone()
+        dist.all_reduce(want, op=dist.ReduceOp.AVG)
+        got = comm.all_reduce(x, op="avg", algo="AUTO")
+        healthy(comm)
+        assert comm.stats().nvls_calls == calls + 1
+        assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+        # replay from a CUDA graph: the use counters live in device memory
+        x = torch.randn(1 << 20, device="cuda")
+        out = torch.empty_like(x)
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            comm.all_reduce(x, out, algo="NVLS", stream=s)
+            s.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=s):
+                comm.all_reduce(x, out, algo="NVLS", stream=s)
+            for i in range(3):
+                x.fill_(float(i + rank))
+                graph.replay()
+                s.synchronize()
+                assert torch.equal(out, torch.full_like(out, float(world * i + world * (world - 1) // 2)))
+        healthy(comm)
     dist.barrier()
     comm.close()
-    print(f"WORKER_OK nvls", flush=True)
 
 
 if __name__ == "__main__":

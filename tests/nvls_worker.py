@@ -2,8 +2,8 @@
 All ranks are virtual ranks of one cooperative launch (LoopbackGroup); a multimem load-reduce becomes a loop over the
 ranks' windows and a multicast store a loop of stores, everything else (chunking, half slots, counters, copies, the
 handling of unaligned buffers and odd sizes) is the code that runs on real NVLink multicast windows.  Results are
-compared with plain PyTorch fp32 arithmetic.  Small half slots (PICCL_NVLS_CHUNK_KB) make every CTA wrap around its two
-half slots many times, and the collectives are interleaved so that a half slot is reused by a different collective."""
+compared with plain PyTorch fp32 arithmetic.  Small slots (PICCL_NVLS_CHUNK_KB) make every CTA wrap around the parts of its
+slot many times, and the collectives are interleaved so that a part is reused by a different collective."""
 import os
 import sys
 from pathlib import Path
@@ -48,7 +48,7 @@ def main():
         for dtype in (torch.float32, torch.bfloat16, torch.float16):
             es = torch.empty(0, dtype=dtype).element_size()
             ops = ("sum", "avg") if dtype == torch.float32 else ("sum", "avg", "max", "min")
-            # element counts: one element; an odd size with a tail; several chunks per CTA (6 CTAs x 2 half slots of 8 KiB)
+            # element counts: one element; an odd size with a tail; several chunks per CTA (6 CTAs, parts of 8 KiB)
             for count in (1, 1001, (200 * 1024) // es + 3):
                 for op in ops:
                     xs = [rand(count, dtype, 10 * r + count % 7) for r in range(n)]
@@ -60,7 +60,7 @@ def main():
                     for r in range(n):
                         assert torch.allclose(outs[r].float(), want, atol=tol(dtype, n), rtol=1e-2), f"allreduce n={n} {dtype} {count} {op} rank {r}: {(outs[r].float() - want).abs().max().item()}"
                         assert torch.equal(outs[r], outs[0]), "ranks differ"
-            # block collectives: blocks of a multiple of 16 bytes take the switch; interleaved so that half slots change hands
+            # block collectives: blocks of a multiple of 16 bytes take the switch; interleaved so that the parts of a slot change hands
             for count in (16 // es, (48 * 1024) // es, (24 * 1024 + 16) // es):
                 xs = [rand(count, dtype, 100 + r) for r in range(n)]
                 # all-gather

@@ -1,12 +1,12 @@
-"""Exhaustive interleaving check of the counter / half-slot protocol of the in-switch collectives
-(src/kernels/nvls_coll.cu, described in src/kernels/nvls.cuh), on a small model: a few ranks, one CTA index, a few chunks,
-several calls of different collectives in a row.
+"""Exhaustive interleaving check of the counter / slot protocol of the in-switch collectives
+(src/kernels/nvls_coll.cu, described in src/kernels/nvls.cuh), on a small model: two ranks, one CTA index with its three
+warp groups (fill, switch, out) running on their own, a few chunks, several calls of different collectives in a row.
 
-Each rank runs the kernel's sequence of phases; the explorer tries every order in which ranks can advance and in which
-counter arrivals can reach each rank (an arrival is delivered to every rank separately, in any order).  Data is modelled
-as tags per (rank's copy, half slot, portion): a fill marks portions "in, chunk", the in-switch sum of an all-reduce
+Every warp group runs the kernel's sequence of phases; the explorer tries every order in which the groups can advance and
+in which counter arrivals can reach each rank (an arrival is delivered to every rank separately, in any order).  Data is
+modelled as tags per (rank's copy, part of the slot, portion): a fill marks portions "in, chunk", the in-switch sum of an all-reduce
 requires "in" in its portion of EVERY copy and marks it "sum" everywhere, a copy-out or a load-reduce requires what it
-reads to be there and marks it "done".  Writing over anything that is not "done" is a violation, so a half slot that is
+reads to be there and marks it "done".  Writing over anything that is not "done" is a violation, so a part that is
 refilled too early (by the same or by another collective) shows up, and a lost wake-up shows up as a deadlock.  The
 release ordering of the real kernel (data before the arrival) is what makes it legal to apply a phase's writes at once,
 before its arrival is issued.  The reference has no counterpart."""
@@ -18,202 +18,194 @@ import pytest
 sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
 
 FILLED, REDUCED, CONSUMED = 0, 1, 2
-N_COUNTERS = 6          # counter index = half * 3 + kind
+MAX_DEPTH = 4
+N_COUNTERS = MAX_DEPTH * 3          # counter index = part * 3 + kind
 
 
-def ctr(half, kind):
-    return half * 3 + kind
+def ctr(part, kind):
+    return part * 3 + kind
 
 
-def program(coll, n, r, m, used, call, root=0, broken=None):
-    """The phases of rank r for one call of `coll` with m chunks, exactly in the order of nvls_coll_kernel.
-    used = [fills of half 0, fills of half 1, reductions of half 0, reductions of half 1] so far; returns (ops, used')."""
-    bu, by = used[:2], used[2:]
-    ops = []
+def programs(coll, n, r, m, used, call, root=0, depth=2, broken=None):
+    """The phases of the three warp groups (fill, switch, out) of rank r for one call of `coll` with m chunks, exactly in the
+    order of nvls_coll_kernel.  used = fills so far of part 0..3, then reductions so far of part 0..3; returns ([fill ops,
+    switch ops, out ops], used')."""
+    bu, by = used[:MAX_DEPTH], used[MAX_DEPTH:]
+    fill, switch, out = [], [], []
     g = lambda j: (call, j)
-
-    def wait_consumed(j):
-        s = j & 1
-        target = n * (bu[s] + (j >> 1))
-        if target and broken != "no_wait_consumed":
-            ops.append(("wait", ctr(s, CONSUMED), target))
-
-    if coll == "allreduce":
-        def fill(j):
-            wait_consumed(j)
-            ops.append(("fill_own", g(j), j & 1))
-            ops.append(("arrive", ctr(j & 1, FILLED), 1))
-        if m > 0:
-            fill(0)
-        for j in range(m):
-            s = j & 1
-            if broken != "no_wait_filled":
-                ops.append(("wait", ctr(s, FILLED), n * (bu[s] + (j >> 1) + 1)))
-            ops.append(("reduce_all", g(j), s, r))
-            ops.append(("arrive", ctr(s, REDUCED), 1))
-            if j + 1 < m:
-                fill(j + 1)
-            if broken != "no_wait_reduced":
-                ops.append(("wait", ctr(s, REDUCED), n * (by[s] + (j >> 1) + 1)))
-            ops.append(("copy_out", g(j), s, "sum"))
-            ops.append(("arrive", ctr(s, CONSUMED), 1))
-        new = [bu[0] + (m + 1) // 2, bu[1] + m // 2, by[0] + (m + 1) // 2, by[1] + m // 2]
-        return ops, new
+    allreduce = coll == "allreduce"
     filler = (r == root) if coll == "broadcast" else True
     consumer = (r == root) if coll == "reduce" else True
     fill_inc = n if coll == "broadcast" else 1
     cons_inc = n if coll == "reduce" else 1
-
-    def fill(j):
-        wait_consumed(j)
-        s = j & 1
-        if coll == "allgather":
-            ops.append(("fill_all", g(j), s, (r,)))
-        elif coll == "broadcast":
-            ops.append(("fill_all", g(j), s, tuple(range(n))))
-        else:
-            ops.append(("fill_own", g(j), s))
-        ops.append(("arrive", ctr(s, FILLED), fill_inc))
-
-    if m > 0 and filler:
-        fill(0)
     for j in range(m):
-        s = j & 1
-        if filler and j + 1 < m:
-            fill(j + 1)
-        if consumer:
-            if broken != "no_wait_filled":
-                ops.append(("wait", ctr(s, FILLED), n * (bu[s] + (j >> 1) + 1)))
-            if coll in ("allgather", "broadcast"):
-                ops.append(("copy_out", g(j), s, "in"))
-            elif coll == "reduce_scatter":
-                ops.append(("reduce_local", g(j), s, (r,)))
+        p, u, uy = j % depth, bu[j % depth] + j // depth, by[j % depth] + j // depth
+        if filler:
+            if n * u and broken != "no_wait_consumed":
+                fill.append(("wait", ctr(p, CONSUMED), n * u))
+            if coll == "allgather":
+                fill.append(("fill_all", g(j), p, (r,)))
+            elif coll == "broadcast":
+                fill.append(("fill_all", g(j), p, tuple(range(n))))
             else:
-                ops.append(("reduce_local", g(j), s, tuple(range(n))))
-            ops.append(("arrive", ctr(s, CONSUMED), cons_inc))
-    return ops, [bu[0] + (m + 1) // 2, bu[1] + m // 2, by[0], by[1]]
+                fill.append(("fill_own", g(j), p))
+            fill.append(("arrive", ctr(p, FILLED), fill_inc))
+        if allreduce:
+            if broken != "no_wait_filled":
+                switch.append(("wait", ctr(p, FILLED), n * (u + 1)))
+            switch.append(("reduce_all", g(j), p, r))
+            switch.append(("arrive", ctr(p, REDUCED), 1))
+        if consumer:
+            if allreduce:
+                if broken != "no_wait_reduced":
+                    out.append(("wait", ctr(p, REDUCED), n * (uy + 1)))
+                out.append(("copy_out", g(j), p, "sum"))
+            else:
+                if broken != "no_wait_filled":
+                    out.append(("wait", ctr(p, FILLED), n * (u + 1)))
+                if coll in ("allgather", "broadcast"):
+                    out.append(("copy_out", g(j), p, "in"))
+                elif coll == "reduce_scatter":
+                    out.append(("reduce_local", g(j), p, (r,)))
+                else:
+                    out.append(("reduce_local", g(j), p, tuple(range(n))))
+            out.append(("arrive", ctr(p, CONSUMED), cons_inc))
+    cnt = [(m + depth - 1 - p) // depth if p < depth else 0 for p in range(MAX_DEPTH)]
+    new = [bu[p] + cnt[p] for p in range(MAX_DEPTH)] + [by[p] + (cnt[p] if allreduce else 0) for p in range(MAX_DEPTH)]
+    return [fill, switch, out], new
 
 
-def sequence(n, calls, broken=None):
-    """calls: list of (collective, chunks, root).  Returns the per-rank programs of the whole sequence."""
-    progs = [[] for _ in range(n)]
-    used = [0, 0, 0, 0]
+def sequence(n, calls, depth=2, broken=None):
+    """calls: list of (collective, chunks, root).  Returns the programs of the whole sequence, one per (rank, warp group):
+    kernels of one rank run one after the other, so a group's ops of call k+1 follow ALL groups' ops of call k; that is
+    modelled with a local barrier between calls."""
+    procs = [[] for _ in range(3 * n)]
+    used = [0] * (2 * MAX_DEPTH)
     for ci, (coll, m, root) in enumerate(calls):
         nxt = None
         for r in range(n):
-            ops, nxt = program(coll, n, r, m, used, ci, root, broken)
-            progs[r] += ops
+            roles, nxt = programs(coll, n, r, m, used, ci, root, depth, broken)
+            for k in range(3):
+                procs[3 * r + k] += roles[k] + [("kernel_end", ci)]
         used = nxt
-    return progs, used
+    return procs, used
 
 
-def explore(n, programs, limit=4_000_000):
+def explore(n, procs, limit=6_000_000):
     """Returns the number of states visited; raises AssertionError naming the violation or the deadlock."""
-    # arrivals issued by src on counter c, in program order, as (position in the program, increment)
-    arrivals = [[[(i, op[2]) for i, op in enumerate(programs[src]) if op[0] == "arrive" and op[1] == c] for c in range(N_COUNTERS)] for src in range(n)]
-    start = (tuple([0] * n), tuple([0] * (n * N_COUNTERS * n)), tuple([None] * (n * 2 * n)))
+    P = len(procs)
+    # arrivals issued by process s on counter c, in program order, as (position in the program, increment)
+    arrivals = [[[(i, op[2]) for i, op in enumerate(procs[s]) if op[0] == "arrive" and op[1] == c] for c in range(N_COUNTERS)] for s in range(P)]
+    live = [(s, c) for s in range(P) for c in range(N_COUNTERS) if arrivals[s][c]]
+    idx = {sc: k for k, sc in enumerate(live)}
+    start = (tuple([0] * P), tuple([0] * (len(live) * n)), tuple([None] * (n * MAX_DEPTH * n)))
     seen = {start}
     stack = [start]
     free = lambda tag: tag is None or tag[0] == "done"
+    at = lambda q, h, p: (q * MAX_DEPTH + h) * n + p
     while stack:
         pcs, deliv, tags = stack.pop()
         succ = []
-        for src in range(n):
-            for c in range(N_COUNTERS):
-                issued = sum(1 for pos, _ in arrivals[src][c] if pos < pcs[src])
-                for dst in range(n):
-                    i = (src * N_COUNTERS + c) * n + dst
-                    if deliv[i] < issued:
-                        d = list(deliv); d[i] += 1
-                        succ.append((pcs, tuple(d), tags))
-        for r in range(n):
-            if pcs[r] >= len(programs[r]):
+        for (s_, c), k in idx.items():
+            issued = sum(1 for pos, _ in arrivals[s_][c] if pos < pcs[s_])
+            for dst in range(n):
+                i = k * n + dst
+                if deliv[i] < issued:
+                    d = list(deliv); d[i] += 1
+                    succ.append((pcs, tuple(d), tags))
+        for pr in range(P):
+            if pcs[pr] >= len(procs[pr]):
                 continue
-            op = programs[r][pcs[r]]
+            r = pr // 3
+            op = procs[pr][pcs[pr]]
             t = list(tags)
-            at = lambda q, h, p: (q * 2 + h) * n + p
             if op[0] == "wait":
-                have = sum(sum(inc for _, inc in arrivals[src][op[1]][:deliv[(src * N_COUNTERS + op[1]) * n + r]]) for src in range(n))
+                have = sum(sum(inc for _, inc in arrivals[s_][c][:deliv[k * n + r]]) for (s_, c), k in idx.items() if c == op[1])
                 if have < op[2]:
+                    continue
+            elif op[0] == "kernel_end":
+                # the next kernel of this rank starts when every group of this one is done
+                if any(not (pcs[3 * r + k] < len(procs[3 * r + k]) and procs[3 * r + k][pcs[3 * r + k]] == op) and
+                       not any(o == op for o in procs[3 * r + k][:pcs[3 * r + k]]) for k in range(3)):
                     continue
             elif op[0] == "fill_own":
                 _, g, h = op
                 for p in range(n):
-                    assert free(t[at(r, h, p)]), f"rank {r} fills half {h} with {g} over {t[at(r, h, p)]}"
+                    assert free(t[at(r, h, p)]), f"rank {r} fills part {h} with {g} over {t[at(r, h, p)]}"
                     t[at(r, h, p)] = ("in", g)
             elif op[0] == "fill_all":
                 _, g, h, portions = op
                 for q in range(n):
                     for p in portions:
-                        assert free(t[at(q, h, p)]), f"rank {r} stores {g} into portion {p} of rank {q}'s half {h} over {t[at(q, h, p)]}"
+                        assert free(t[at(q, h, p)]), f"rank {r} stores {g} into portion {p} of rank {q}'s part {h} over {t[at(q, h, p)]}"
                         t[at(q, h, p)] = ("in", g)
             elif op[0] == "reduce_all":
                 _, g, h, p = op
                 for q in range(n):
-                    assert t[at(q, h, p)] == ("in", g), f"rank {r} sums {g} but rank {q}'s half {h} holds {t[at(q, h, p)]}"
+                    assert t[at(q, h, p)] == ("in", g), f"rank {r} sums {g} but rank {q}'s part {h} holds {t[at(q, h, p)]}"
                 for q in range(n):
                     t[at(q, h, p)] = ("sum", g)
             elif op[0] == "copy_out":
                 _, g, h, want = op
                 for p in range(n):
-                    assert t[at(r, h, p)] == (want, g), f"rank {r} copies {g} out of half {h} but portion {p} holds {t[at(r, h, p)]}"
+                    assert t[at(r, h, p)] == (want, g), f"rank {r} copies {g} out of part {h} but portion {p} holds {t[at(r, h, p)]}"
                     t[at(r, h, p)] = ("done", g)
             elif op[0] == "reduce_local":
                 _, g, h, portions = op
                 for q in range(n):
                     for p in portions:
-                        assert t[at(q, h, p)] == ("in", g), f"rank {r} load-reduces {g} but portion {p} of rank {q}'s half {h} holds {t[at(q, h, p)]}"
+                        assert t[at(q, h, p)] == ("in", g), f"rank {r} load-reduces {g} but portion {p} of rank {q}'s part {h} holds {t[at(q, h, p)]}"
                 for q in range(n):
                     for p in portions:
                         t[at(q, h, p)] = ("done", g)
-            p2 = list(pcs); p2[r] += 1
+            p2 = list(pcs); p2[pr] += 1
             succ.append((tuple(p2), deliv, tuple(t)))
         if not succ:
-            assert all(pcs[r] == len(programs[r]) for r in range(n)), f"deadlock at {pcs}: {[programs[r][pcs[r]] for r in range(n) if pcs[r] < len(programs[r])]}"
-        for s in succ:
-            if s not in seen:
-                seen.add(s)
-                stack.append(s)
+            assert all(pcs[k] == len(procs[k]) for k in range(P)), f"deadlock at {pcs}: {[procs[k][pcs[k]] for k in range(P) if pcs[k] < len(procs[k])]}"
+        for st in succ:
+            if st not in seen:
+                seen.add(st)
+                stack.append(st)
                 assert len(seen) < limit, "state space larger than expected"
     return len(seen)
 
 
-@pytest.mark.parametrize("calls", [
-    [("allreduce", 3, 0), ("allreduce", 2, 0)],
-    [("allreduce", 2, 0), ("allgather", 3, 0)],
-    [("allgather", 3, 0), ("allreduce", 2, 0)],
-    [("reduce_scatter", 3, 0), ("allreduce", 2, 0)],
-    [("broadcast", 3, 1), ("reduce", 3, 0)],
-    [("reduce", 2, 1), ("allgather", 2, 0), ("broadcast", 2, 0)],
-    [("allreduce", 1, 0), ("reduce_scatter", 2, 0), ("allgather", 1, 0)],
+@pytest.mark.parametrize("calls,depth", [
+    ([("allreduce", 3, 0)], 2),
+    ([("allreduce", 2, 0), ("allreduce", 1, 0)], 2),
+    ([("allreduce", 1, 0), ("allgather", 2, 0)], 2),
+    ([("allgather", 3, 0)], 2),
+    ([("allgather", 1, 0), ("allreduce", 1, 0)], 2),
+    ([("reduce_scatter", 3, 0)], 2),
+    ([("reduce_scatter", 1, 0), ("allreduce", 1, 0)], 2),
+    ([("broadcast", 3, 1)], 2),
+    ([("broadcast", 1, 1), ("reduce", 2, 0)], 2),
+    ([("reduce", 3, 1)], 2),
+    ([("allgather", 4, 0)], 3),
 ])
-def test_every_interleaving_of_two_ranks_is_safe_and_terminates(calls):
-    progs, _ = sequence(2, calls)
-    assert explore(2, progs) > 50
+def test_every_interleaving_of_two_ranks_is_safe_and_terminates(calls, depth):
+    procs, _ = sequence(2, calls, depth)
+    assert explore(2, procs) > 20
 
 
-@pytest.mark.parametrize("calls", [[("allreduce", 1, 0)], [("allgather", 1, 0)], [("reduce_scatter", 1, 0)], [("broadcast", 1, 2)], [("reduce", 1, 1)], [("broadcast", 1, 0), ("reduce", 1, 2)]])
-def test_three_ranks(calls):
-    progs, _ = sequence(3, calls)
-    explore(3, progs)
-
-
-def test_odd_and_even_chunk_counts_keep_the_half_slot_counters_in_step():
-    # 3 chunks then 2 chunks: half slot 0 was used twice, half slot 1 once, before the second call
-    progs, used = sequence(2, [("allreduce", 3, 0), ("allgather", 2, 0)])
-    assert used == [3, 2, 2, 1]
-    explore(2, progs)
+def test_counts_of_uses_stay_in_step_for_any_number_of_chunks():
+    # 3 chunks on a slot of 2 parts, then 2 chunks: part 0 was used twice, part 1 once, before the second call
+    procs, used = sequence(2, [("allreduce", 3, 0), ("allgather", 2, 0)], depth=2)
+    assert used == [3, 2, 0, 0, 2, 1, 0, 0]
+    _, used = sequence(2, [("allreduce", 5, 0)], depth=4)
+    assert used == [2, 1, 1, 1, 2, 1, 1, 1]
 
 
 @pytest.mark.parametrize("calls,broken", [
     ([("allreduce", 3, 0)], "no_wait_filled"),
     ([("allreduce", 3, 0)], "no_wait_reduced"),
-    ([("allgather", 3, 0)], "no_wait_consumed"),          # the third chunk is stored over the first before it was copied out
-    ([("allreduce", 1, 0), ("allgather", 1, 0)], "no_wait_consumed"),   # another collective takes the half slot over too early
+    ([("allreduce", 3, 0)], "no_wait_consumed"),          # the third chunk is staged over the first before it was copied out
+    ([("allgather", 3, 0)], "no_wait_consumed"),          # ... or stored over it in a peer's copy
+    ([("allreduce", 1, 0), ("allgather", 1, 0)], "no_wait_consumed"),   # another collective takes the part over too early
     ([("reduce_scatter", 3, 0)], "no_wait_consumed"),     # the own copy is refilled while a peer still load-reduces from it
     ([("broadcast", 2, 0)], "no_wait_filled"),
 ])
 def test_the_checker_finds_a_missing_wait(calls, broken):
-    progs, _ = sequence(2, calls, broken=broken)
+    procs, _ = sequence(2, calls, depth=2, broken=broken)
     with pytest.raises(AssertionError):
-        explore(2, progs)
+        explore(2, procs)
