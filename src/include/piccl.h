@@ -48,7 +48,8 @@ typedef struct { unsigned char bytes[128]; } piccl_handle_t;
 typedef struct {
   int aborted;      /* 1 after a device-side wait ran out or piccl_comm_abort() */
   int code;         /* 1: wait for FIFO credit, 2: wait for FIFO data, 3: aborted by host/peer CTA,
-                       5 / 6 / 7: in-switch collective, wait for a chunk to be filled / reduced / consumed by all ranks (segment = chunk) */
+                       5 / 6 / 7: in-switch collective, wait for a chunk to be filled / reduced / consumed by all ranks (segment = chunk);
+                       8: in-switch collective, a bulk copy did not arrive */
   int rank, cta, action, peer, segment;
   unsigned long long want, have;   /* counter value waited for / last seen */
 } piccl_status_t;

@@ -11,8 +11,8 @@
 //   [ kNvlsFlagBytes: counters, three per (CTA index, part of its slot), 128 bytes apart ]
 //   [ one slot of slot_bytes per CTA index, used as `depth` parts ]
 // CTA b of every rank works on chunks b, b + n_cta, ... of the message; chunk j of a CTA goes
-// through part j % depth of its slot, and three groups of warps of the CTA (fill, switch, out) work
-// on different chunks at the same time.
+// through part j % depth of its slot, and the groups of warps of the CTA (fill, switch, out; the one
+// that talks to the switch split further) work on different chunks at the same time.
 // One use of a part has up to three stages, each closed by one counter that every rank
 // raises (by n in total) on all copies with a single multimem.red:
 //   FILLED    the chunk is in the part            (all-reduce, reduce-scatter, reduce: every rank copied its own
@@ -40,10 +40,10 @@
 namespace piccl {
 
 constexpr int kNvlsMaxCta = 128;
-constexpr int kNvlsMaxDepth = 4;          // parts per slot, at most
-constexpr int kNvlsFlagBytes = 262144;    // 128 CTA indices x 4 parts x 3 counters x 128 bytes = 192 KiB, rounded up
+constexpr int kNvlsMaxDepth = 8;          // parts per slot, at most
+constexpr int kNvlsFlagBytes = 524288;    // 128 CTA indices x 8 parts x 3 counters x 128 bytes = 384 KiB, rounded up
 constexpr int kNvlsBlock = 512;
-constexpr int kNvlsUsedPerCta = 2 * kNvlsMaxDepth;   // uses so far per CTA index: fills of part 0..3, then reductions (all-reduce) of part 0..3
+constexpr int kNvlsUsedPerCta = 2 * kNvlsMaxDepth;   // uses so far per CTA index: fills of part 0..7, then reductions (all-reduce) of part 0..7
 enum NvlsCounter : int { NVC_FILLED = 0, NVC_REDUCED = 1, NVC_CONSUMED = 2 };
 
 struct NvlsRank {
@@ -63,12 +63,14 @@ struct NvlsArgs {
   int coll, nranks, n_cta, n_vrank;
   int avg, root;
   float scale;
-  int pad;
   long long bytes;                        // all-reduce, broadcast, reduce: message bytes; all-gather, reduce-scatter: bytes of one rank's block
   long long chunk_bytes;                  // bytes of the message (or of each rank's block) per chunk; a multiple of 16, of 16 * nranks for all-reduce
   long long sub_stride;                   // all-gather, reduce-scatter: distance between two ranks' pieces inside a part (>= chunk_bytes, multiple of 16)
   long long slot_bytes;                   // distance between two slots; a part is slot_bytes / depth (multiple of 16)
-  int depth, pad2;                        // parts per slot (2 .. kNvlsMaxDepth): chunks a CTA has in flight
+  int depth;                              // parts per slot (2 .. kNvlsMaxDepth): chunks a CTA has in flight
+  int n_sub;                              // groups the stage that issues the multimem instructions is split into (1 or 3)
+  int strict_fences;                      // 1: a system-wide fence before every counter update (see nv_arrive)
+  int use_bulk;                           // 1: aligned copies between user buffers and the window go through the bulk-copy engine (TMA)
   unsigned long long timeout_ns;
   NvlsRank r[kMaxVRanks];
 };

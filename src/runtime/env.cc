@@ -43,12 +43,15 @@ static void load() {
   e.tp_feeders = env_int("PICCL_TP_FEEDERS", 24); // CTAs that push the local shard in all-gather -> GEMM
   e.exec_defer = env_int("PICCL_EXEC_DEFER", 0);
   e.nvls = env_int("PICCL_NVLS", 1);            // 0: no NVLink multicast window (algorithm NVLS then runs the peer-to-peer schedules)
-  e.nvls_chunk_kb = env_int("PICCL_NVLS_CHUNK_KB", 128);   // largest chunk = one part of a CTA's slot
-  e.nvls_depth = env_int("PICCL_NVLS_DEPTH", 4);           // parts per slot (2 .. 4): chunks a CTA has in flight in its three stages
+  e.nvls_chunk_kb = env_int("PICCL_NVLS_CHUNK_KB", 256);   // largest chunk = one part of a CTA's slot
+  e.nvls_depth = env_int("PICCL_NVLS_DEPTH", 5);           // parts per slot (2 .. 8): chunks a CTA has in flight in its stages
   e.nvls_cta = env_int("PICCL_NVLS_CTA", 128);             // CTAs (= slots of the window) of an in-switch collective
-  e.nvls_auto_kb = env_int("PICCL_NVLS_AUTO_KB", 256);     // AUTO sends messages above this size through the switch when a window exists
+  e.nvls_auto_kb = env_int("PICCL_NVLS_AUTO_KB", 1024);    // AUTO sends all-reduces above this size (all-gathers / reduce-scatters above a quarter of it in total) through the switch
   e.nvls_min_kb = env_int("PICCL_NVLS_MIN_KB", 64);        // a mid-size message is cut into chunks of at least this size before more CTAs are used
   { const char* g = getenv("PICCL_NVLS_GRAN"); e.nvls_gran_min = !(g && !strcmp(g, "recommended")); }
+  e.nvls_bulk = env_int("PICCL_NVLS_BULK", 1);             // 0: copies between user buffers and the window use the threads' loads and stores, not the bulk-copy engine
+  { const char* f = getenv("PICCL_NVLS_FENCE"); e.nvls_strict_fences = f && !strcmp(f, "sys"); }   // sys: a system-wide fence before every counter update of the in-switch kernels
+  e.nvls_sub = env_int("PICCL_NVLS_SUB", 0);               // 1 / 3: groups of the stage that talks to the switch; 0: 3 for large all-reduces on four ranks or more, else 1
   e.nvls_profile = env_int("PICCL_NVLS_PROFILE", 0);       // 1: the kernels sum the time of every phase; printed when the communicator is destroyed
   // PICCL_PROTO narrows the choice of data path that is otherwise made per call by message size:
   //   auto    (default) low-latency kernels for small messages, the FIFO executor otherwise

@@ -6,7 +6,7 @@
 // (default -1), PICCL_BLOCK_SIZE (1024), PICCL_MAX_GRID_SIZE (1024),
 // PICCL_MIN_GRID_SIZE (1).  Additions that do not change those semantics: the
 // value AUTO, PICCL_TIMEOUT_MS, PICCL_SCRATCH_MB, PICCL_SLOT_KB, PICCL_NSLOT,
-// PICCL_MAX_CTA, PICCL_LL_KB, PICCL_LLF_KB, PICCL_TP_MB, PICCL_TP_FEEDERS, PICCL_LAUNCH, PICCL_PERSIST_IDLE_US, PICCL_PROTO, PICCL_EXEC_DEFER, PICCL_NVLS, PICCL_NVLS_CHUNK_KB, PICCL_NVLS_DEPTH, PICCL_NVLS_CTA, PICCL_NVLS_MIN_KB, PICCL_NVLS_AUTO_KB, PICCL_NVLS_GRAN, PICCL_NVLS_PROFILE, PICCL_LOG, PICCL_TRACE, PICCL_FAULT, PICCL_TUNE_FILE, PICCL_DEBUG.
+// PICCL_MAX_CTA, PICCL_LL_KB, PICCL_LLF_KB, PICCL_TP_MB, PICCL_TP_FEEDERS, PICCL_LAUNCH, PICCL_PERSIST_IDLE_US, PICCL_PROTO, PICCL_EXEC_DEFER, PICCL_NVLS, PICCL_NVLS_CHUNK_KB, PICCL_NVLS_DEPTH, PICCL_NVLS_CTA, PICCL_NVLS_MIN_KB, PICCL_NVLS_AUTO_KB, PICCL_NVLS_GRAN, PICCL_NVLS_PROFILE, PICCL_NVLS_BULK, PICCL_NVLS_FENCE, PICCL_NVLS_SUB, PICCL_LOG, PICCL_TRACE, PICCL_FAULT, PICCL_TUNE_FILE, PICCL_DEBUG.
 #pragma once
 #include <string>
 #include "../include/piccl_sched.h"
@@ -22,7 +22,7 @@ struct Env {
   int log_level, debug;
   int exec_defer;                                // PICCL_EXEC_DEFER=1: the FIFO executor publishes counters lazily (exec_impl.cuh)
   int proto;                                     // PICCL_PROTO: 0 auto, 1 ll, 2 simple, 3 nvls (see env.cc)
-  int nvls, nvls_chunk_kb, nvls_depth, nvls_cta, nvls_min_kb, nvls_auto_kb, nvls_gran_min, nvls_profile;           // PICCL_NVLS=0: no multicast window; half-slot size, CTA count and smallest chunk of the in-switch collectives
+  int nvls, nvls_chunk_kb, nvls_depth, nvls_cta, nvls_min_kb, nvls_auto_kb, nvls_gran_min, nvls_profile, nvls_bulk, nvls_strict_fences, nvls_sub;           // PICCL_NVLS=0: no multicast window; half-slot size, CTA count and smallest chunk of the in-switch collectives
   bool launch_persistent; int persist_idle_us;   // PICCL_LAUNCH=persistent, PICCL_PERSIST_IDLE_US
   std::string trace_file, tune_file;
   // host-side fault injection: rank:call:{skip_call|delay_ms=N}

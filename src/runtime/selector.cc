@@ -39,12 +39,18 @@ Algo select_algo_n(int n, Coll coll, size_t bytes, int* k, bool window) {
   std::call_once(g_once, load_table);
   for (auto& r : g_rows)
     if (r.coll == coll && r.nranks == n && (long long)bytes <= r.max_bytes && (window || r.algo != ALGO_NVLS)) { if (k) *k = r.k; return r.algo; }
-  // With a multicast window: everything that is not latency bound goes through the switch (the message crosses each
-  // link about once instead of 2(n-1)/n times, and no step waits for a neighbour's step).  `bytes` is the whole vector
-  // for all-reduce / broadcast / reduce and one rank's block for all-gather / reduce-scatter.
-  if (window && n >= 2) {
-    const size_t total = (coll == COLL_ALLGATHER || coll == COLL_REDUCE_SCATTER) ? bytes * (size_t)n : bytes;
-    if (total > ((size_t)env().nvls_auto_kb << 10)) { if (k) *k = -1; return ALGO_NVLS; }
+  // With a multicast window (four ranks or more; on two ranks the peer-to-peer schedules are ahead at every size: 609 vs 310
+  // GB/s at 1 GiB).  Measured on 8 B200, bus bandwidth in GB/s, in-switch / best peer-to-peer schedule / stock NCCL:
+  //   all-reduce      4 MiB 171 / 104 / 123, 16 MiB 368 / 222 / 279, 64 MiB 517 / 357 / 415, 1 GiB 789 / 617 / 727; up to 1 MiB the
+  //                   low-latency kernel is ahead (27 us against 37 us at 1 MiB)
+  //   all-gather      (per rank) 1 MiB 184 / 74 / 146, 4 MiB 369 / 232 / 361, 16 MiB 490 / 464 / 549, 64 MiB 529 / 598 / 601
+  //   reduce-scatter  (per rank) 1 MiB 200 / 80 / 153, 4 MiB 400 / 239 / 373, 16 MiB 542 / 466 / 550, 64 MiB 590 / 601 / 602
+  //   broadcast, reduce   the root's multicast stores / load-reduces are the bottleneck (340 GB/s): the pipelined chain stays
+  // `bytes` is the whole vector for all-reduce / broadcast / reduce and one rank's block for all-gather / reduce-scatter.
+  if (window && n >= 4) {
+    const size_t lo = (size_t)env().nvls_auto_kb << 10;
+    if (coll == COLL_ALLREDUCE && bytes > lo) { if (k) *k = -1; return ALGO_NVLS; }
+    if ((coll == COLL_ALLGATHER || coll == COLL_REDUCE_SCATTER) && bytes * (size_t)n > lo / 4 && bytes <= ((size_t)32 << 20)) { if (k) *k = -1; return ALGO_NVLS; }
   }
   // Built-in rule, from sweeps on 2, 4 and 8 B200 (fp32 and bf16 sum):
   //   all-reduce      <= 4 KiB one exchange with every rank (PRM, k = n: 8 us on 8 GPUs); up to 32 MiB (8 MiB on two

@@ -281,13 +281,13 @@ def case_nvls(rank, world):
                 assert torch.allclose(r_out.float(), r_ref.float(), atol=tol(dtype, world), rtol=1e-2), f"nvls reduce {dtype} {count}"
             calls += 4
         assert comm.stats().nvls_calls == calls, (comm.stats().nvls_calls, calls)
-        # AUTO takes the switch for large messages
+        # AUTO takes the switch for large messages from four ranks on
         x = rand(8 << 20, torch.bfloat16, 700 + rank)
         want = x.clone()
         dist.all_reduce(want, op=dist.ReduceOp.AVG)
         got = comm.all_reduce(x, op="avg", algo="AUTO")
         healthy(comm)
-        assert comm.stats().nvls_calls == calls + 1
+        assert comm.stats().nvls_calls == calls + (1 if world >= 4 else 0)
         assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
         # replay from a CUDA graph: the use counters live in device memory
         x = torch.randn(1 << 20, device="cuda")

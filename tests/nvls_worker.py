@@ -137,12 +137,12 @@ def main():
         healthy("int32 odd all-gather")
         assert torch.equal(outs[n - 1], torch.cat(xi))
         assert grp.stats().nvls_calls - before == calls
-        # AUTO picks the switch for large messages when a window exists
+        # AUTO picks the switch for large messages when a window exists and there are at least four ranks
         big = [rand(1 << 20, torch.bfloat16, 700 + r) for r in range(n)]
         outs = [torch.empty_like(x) for x in big]
         grp.run("allreduce", big, outs, 1 << 20, op="sum", algo="AUTO")
         healthy("auto")
-        assert grp.stats().nvls_calls - before == calls + 1
+        assert grp.stats().nvls_calls - before == calls + (1 if n >= 4 else 0)
         assert torch.allclose(outs[0].float(), reduce_ref(big, "sum"), atol=tol(torch.bfloat16, n), rtol=1e-2)
         grp.close()
     print(f"NVLS_EMULATED_OK {expected_switch_calls} collectives through the emulated switch")

@@ -1,6 +1,6 @@
 """Exhaustive interleaving check of the counter / slot protocol of the in-switch collectives
-(src/kernels/nvls_coll.cu, described in src/kernels/nvls.cuh), on a small model: two ranks, one CTA index with its three
-warp groups (fill, switch, out) running on their own, a few chunks, several calls of different collectives in a row.
+(src/kernels/nvls_coll.cu, described in src/kernels/nvls.cuh), on a small model: two ranks, one CTA index with its
+warp groups (fill, switch, out; the one that talks to the switch split in two) running on their own, a few chunks, several calls of different collectives in a row.
 
 Every warp group runs the kernel's sequence of phases; the explorer tries every order in which the groups can advance and
 in which counter arrivals can reach each rank (an arrival is delivered to every rank separately, in any order).  Data is
@@ -26,12 +26,17 @@ def ctr(part, kind):
     return part * 3 + kind
 
 
+SUB = 2                 # groups the stage that talks to the switch is split into (3 in the kernel; 2 keeps the state space small)
+
+
 def programs(coll, n, r, m, used, call, root=0, depth=2, broken=None):
-    """The phases of the three warp groups (fill, switch, out) of rank r for one call of `coll` with m chunks, exactly in the
-    order of nvls_coll_kernel.  used = fills so far of part 0..3, then reductions so far of part 0..3; returns ([fill ops,
-    switch ops, out ops], used')."""
+    """The phases of the warp groups (fill, switch, out; the stage that issues the multimem instructions split into SUB groups
+    that take the chunks in turn) of rank r for one call of `coll` with m chunks, exactly in the order of nvls_coll_kernel.
+    used = fills so far of part 0..3, then reductions so far of part 0..3; returns (list of op lists, one per group, used')."""
     bu, by = used[:MAX_DEPTH], used[MAX_DEPTH:]
-    fill, switch, out = [], [], []
+    split = {"allreduce": "switch", "allgather": "fill", "broadcast": "fill", "reduce_scatter": "out", "reduce": "out"}[coll]
+    groups = {"fill": [[] for _ in range(SUB if split == "fill" else 1)], "switch": [[] for _ in range(SUB if split == "switch" else 1)],
+              "out": [[] for _ in range(SUB if split == "out" else 1)]}
     g = lambda j: (call, j)
     allreduce = coll == "allreduce"
     filler = (r == root) if coll == "broadcast" else True
@@ -40,6 +45,7 @@ def programs(coll, n, r, m, used, call, root=0, depth=2, broken=None):
     cons_inc = n if coll == "reduce" else 1
     for j in range(m):
         p, u, uy = j % depth, bu[j % depth] + j // depth, by[j % depth] + j // depth
+        fill, switch, out = (groups[k][j % len(groups[k])] for k in ("fill", "switch", "out"))
         if filler:
             if n * u and broken != "no_wait_consumed":
                 fill.append(("wait", ctr(p, CONSUMED), n * u))
@@ -72,21 +78,22 @@ def programs(coll, n, r, m, used, call, root=0, depth=2, broken=None):
             out.append(("arrive", ctr(p, CONSUMED), cons_inc))
     cnt = [(m + depth - 1 - p) // depth if p < depth else 0 for p in range(MAX_DEPTH)]
     new = [bu[p] + cnt[p] for p in range(MAX_DEPTH)] + [by[p] + (cnt[p] if allreduce else 0) for p in range(MAX_DEPTH)]
-    return [fill, switch, out], new
+    return groups["fill"] + groups["switch"] + groups["out"], new
 
 
 def sequence(n, calls, depth=2, broken=None):
     """calls: list of (collective, chunks, root).  Returns the programs of the whole sequence, one per (rank, warp group):
     kernels of one rank run one after the other, so a group's ops of call k+1 follow ALL groups' ops of call k; that is
     modelled with a local barrier between calls."""
-    procs = [[] for _ in range(3 * n)]
+    G = 2 + SUB                                   # groups per rank
+    procs = [[] for _ in range(G * n)]
     used = [0] * (2 * MAX_DEPTH)
     for ci, (coll, m, root) in enumerate(calls):
         nxt = None
         for r in range(n):
             roles, nxt = programs(coll, n, r, m, used, ci, root, depth, broken)
-            for k in range(3):
-                procs[3 * r + k] += roles[k] + [("kernel_end", ci)]
+            for k in range(G):
+                procs[G * r + k] += roles[k] + [("kernel_end", ci)]
         used = nxt
     return procs, used
 
@@ -116,7 +123,8 @@ def explore(n, procs, limit=6_000_000):
         for pr in range(P):
             if pcs[pr] >= len(procs[pr]):
                 continue
-            r = pr // 3
+            G = P // n
+            r = pr // G
             op = procs[pr][pcs[pr]]
             t = list(tags)
             if op[0] == "wait":
@@ -125,8 +133,8 @@ def explore(n, procs, limit=6_000_000):
                     continue
             elif op[0] == "kernel_end":
                 # the next kernel of this rank starts when every group of this one is done
-                if any(not (pcs[3 * r + k] < len(procs[3 * r + k]) and procs[3 * r + k][pcs[3 * r + k]] == op) and
-                       not any(o == op for o in procs[3 * r + k][:pcs[3 * r + k]]) for k in range(3)):
+                if any(not (pcs[G * r + k] < len(procs[G * r + k]) and procs[G * r + k][pcs[G * r + k]] == op) and
+                       not any(o == op for o in procs[G * r + k][:pcs[G * r + k]]) for k in range(G)):
                     continue
             elif op[0] == "fill_own":
                 _, g, h = op
@@ -181,7 +189,7 @@ def explore(n, procs, limit=6_000_000):
     ([("broadcast", 3, 1)], 2),
     ([("broadcast", 1, 1), ("reduce", 2, 0)], 2),
     ([("reduce", 3, 1)], 2),
-    ([("allgather", 4, 0)], 3),
+    ([("reduce", 4, 1)], 3),
 ])
 def test_every_interleaving_of_two_ranks_is_safe_and_terminates(calls, depth):
     procs, _ = sequence(2, calls, depth)
