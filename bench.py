@@ -15,7 +15,13 @@ Rank 0 prints one JSON line.  `value` is the aggregate tokens/s over all GPUs wi
 already on the device, timed with CUDA events, max over ranks; `e2e` is the same through
 `piccl_b200.train.DataParallelTrainer.step`, whose timed region includes, every step, the copy of
 the batch from pinned host memory and the read-back of the loss.  For N > 1 the line also carries
-all-reduce bus bandwidth / latency at a few message sizes (`collectives`).
+`dropin`: stock PyTorch DDP on the SAME model code as the reference arm (benchmarks/torch_gpt2.py) with this
+    library loaded through LD_PRELOAD and PICCL_ALLREDUCE_ALGO=AUTO, tokens/s and the interposer's counters of
+    calls it ran itself / handed to NCCL;
+`collectives`: all-reduce latency (us) per message size for every algorithm of this library, for stock NCCL and
+    for the reference's own algorithms (fp32; it has no bf16), measured by benchmarks/coll_bench.cc (one process
+    per GPU, CUDA events, maximum over ranks, 1000 / 100 iterations below / from 1 MB, data checked).
+Both run as child processes of rank 0 once the training job has left the GPUs.
 """
 from __future__ import annotations
 
@@ -42,7 +48,8 @@ def parse():
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--algo", default=None, help="all-reduce algorithm of the bucket reductions (RING, K_RING, RD, RM, PRD, PRM, DIRECT, AUTO)")
     ap.add_argument("--k", type=int, default=-1)
-    ap.add_argument("--no-collectives", action="store_true", help="skip the all-reduce sweep for N > 1")
+    ap.add_argument("--no-collectives", action="store_true", help="skip the all-reduce tables for N > 1")
+    ap.add_argument("--no-dropin", action="store_true", help="skip the LD_PRELOAD drop-in run for N > 1")
     return ap.parse_args()
 
 
@@ -104,26 +111,112 @@ def host_batches(cfg, micro_batch: int, n: int, seed: int):
     return out
 
 
-def allreduce_sweep(comm, world: int):
-    """busBW (GB/s) and latency (us) of the fused all-reduce, bf16 sum, device timed, max over ranks."""
-    import torch
-    import torch.distributed as dist
-    res = []
-    for nbytes, algo, k in [(8, "PRM", 8), (64 << 10, "PRM", 8), (25 << 20, "RING", -1), (256 << 20, "RING", -1)]:
-        n = max(1, nbytes // 2)
-        x = torch.ones(n, dtype=torch.bfloat16, device="cuda")
-        iters = 200 if nbytes < (1 << 20) else 20
-        for _ in range(5):
-            comm.all_reduce(x, algo=algo, k=min(k, world) if k > 0 else k)
-        torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(iters):
-            comm.all_reduce(x, algo=algo, k=min(k, world) if k > 0 else k)
-        b.record(); torch.cuda.synchronize()
-        us = max_over_ranks(a.elapsed_time(b) * 1e3 / iters, world)
-        res.append({"bytes": nbytes, "algo": algo, "us": round(us, 2), "busbw_gbs": round(2 * (world - 1) / world * nbytes / us / 1e3, 2)})
-    return res
+def _child_env(extra=None):
+    """Environment for a child job: nothing of this torchrun's rendezvous, nothing preloaded unless asked for."""
+    env = {k: v for k, v in os.environ.items() if not (k.startswith("TORCHELASTIC") or k in (
+        "RANK", "LOCAL_RANK", "WORLD_SIZE", "LOCAL_WORLD_SIZE", "GROUP_RANK", "ROLE_RANK", "ROLE_WORLD_SIZE", "GROUP_WORLD_SIZE", "ROLE_NAME",
+        "MASTER_PORT", "LD_PRELOAD", "PICCL_BENCH_UNDER_REFERENCE", "PICCL_BENCH_LABEL"))}
+    env["MASTER_ADDR"] = "127.0.0.1"
+    env.update(extra or {})
+    return env
+
+
+def _free_port():
+    import socket
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        return sk.getsockname()[1]
+
+
+def run_dropin(args, world: int):
+    """Stock PyTorch DDP (the reference arm's model and optimizer) with this library preloaded, AUTO all-reduce."""
+    import subprocess
+    from piccl_b200 import build
+    so = str(build.lib_path("piccl.so"))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+           str(ROOT / "bench.py"), "--impl", "ddp", "--preload", so, "--gpus", str(world), "--steps", str(args.steps), "--warmup", str(args.warmup), "--model", args.model,
+           "--micro-batch", str(args.micro_batch)]
+    algo = args.algo or "AUTO"
+    try:
+        r = subprocess.run(cmd, env=_child_env({"PICCL_ALLREDUCE_ALGO": algo}), capture_output=True, text=True, timeout=900)
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+    for ln in reversed(r.stdout.strip().splitlines()):
+        if ln.startswith("{"):
+            try:
+                d = json.loads(ln)
+            except ValueError:
+                continue
+            keep = {"value": d.get("value"), "unit": d.get("unit"), "ms_per_step": d.get("ms_per_step"), "e2e": d.get("e2e"), "shim": d.get("shim"),
+                    "stack": "torch DistributedDataParallel + fused AdamW on benchmarks/torch_gpt2.py, LD_PRELOAD=piccl.so", "allreduce_algo_env": algo}
+            return keep
+    return {"unavailable": f"rc {r.returncode}: " + (r.stderr.strip().splitlines() or ["no output"])[-1][:200]}
+
+
+COLL_SIZES = [8, 4096, 65536, 1 << 20, 16 << 20, 25 << 20, 256 << 20, 1 << 30]
+
+
+def run_collectives(world: int):
+    """All-reduce latency per size: every algorithm of this library, stock NCCL and the reference's algorithms (fp32 only),
+    same harness binary, only LD_PRELOAD and PICCL_* differ."""
+    import subprocess
+    from piccl_b200 import build
+    cb = build.lib_path("coll_bench")
+    ours = str(build.lib_path("piccl.so"))
+    if not cb.exists():
+        return {"unavailable": "coll_bench not built"}
+    ref_missing = ensure_reference()
+    ref = str(reference_paths())
+    sizes = ",".join(str(b) for b in COLL_SIZES)
+    table = {"sizes_bytes": COLL_SIZES, "iters": "1000 below 1 MB, 100 from 1 MB", "unit": "us per call, max over ranks", "failed_checks": 0}
+
+    def bench(dtype, label, preload, env_extra, algos=None):
+        cmd = [str(cb), "--gpus", str(world), "--coll", "allreduce", "--dtype", dtype, "--sizes", sizes, "--check", "--label", label]
+        if algos:
+            cmd += ["--algos", algos]
+        env = _child_env(env_extra)
+        if preload:
+            env["LD_PRELOAD"] = preload
+        try:
+            r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+        except Exception as e:  # noqa: BLE001
+            return {label: f"{type(e).__name__}"}
+        rows = {}
+        for ln in r.stdout.splitlines():
+            f = ln.split(",")
+            if len(f) == 11 and f[0] == "allreduce":
+                rows.setdefault(f[1], {})[int(f[5])] = round(float(f[7]), 1)
+                if f[10] == "FAIL":
+                    table["failed_checks"] += 1
+        if not rows:
+            return {label: f"no rows (rc {r.returncode})"}
+        return {k: [v.get(b) for b in COLL_SIZES] for k, v in rows.items()}
+
+    algos = "RING,K_RING:2,K_RING:4,PRD,PRM:2,PRM:4,AUTO"
+    for dtype in ("float", "bf16"):
+        t = {}
+        t.update(bench(dtype, "nccl", "", {}))
+        t.update(bench(dtype, "ours", ours, {}, algos))
+        if dtype == "float":
+            if ref_missing:
+                t["ref"] = ref_missing
+            else:
+                for algo, k in (("RING", None), ("K_RING", 2), ("K_RING", 4), ("PRD", None), ("PRM", 2), ("PRM", 4)):
+                    e = {"PICCL_ALLREDUCE_ALGO": algo}
+                    if k:
+                        e["PICCL_ALLREDUCE_K"] = str(k)
+                    t.update(bench(dtype, f"ref-{algo}" + (f"-k{k}" if k else ""), ref, e))
+        table[dtype] = t
+    # bus bandwidth of AUTO against the comparators at the sizes that matter for gradient buckets and large messages
+    summary = {}
+    for dtype in ("float", "bf16"):
+        t = table.get(dtype, {})
+        auto, nccl = t.get("ours-AUTO-k-1"), t.get("nccl")
+        if isinstance(auto, list) and isinstance(nccl, list):
+            summary[dtype] = {str(b): {"auto_busbw_gbs": round(2 * (world - 1) / world * b / a / 1e3, 1), "nccl_busbw_gbs": round(2 * (world - 1) / world * b / c / 1e3, 1)}
+                              for b, a, c in zip(COLL_SIZES, auto, nccl) if a and c and b >= (1 << 20)}
+    table["busbw_summary"] = summary
+    return table
 
 
 # ------------------------------------------------------------------------------------------------ our arm
@@ -167,10 +260,25 @@ def run_piccl(args):
     launches = (trainer.kernel_launches() - l0) // max(1, args.steps + args.warmup) * args.steps
     ms_e2e, wall_e2e, last_loss = timed_region(step_e2e, args.steps, max(1, args.warmup // 2), world)
     clocks = sampler.stop() if sampler else None
-    coll = allreduce_sweep(comm, world) if (comm is not None and not args.no_collectives) else None
     h2d = 2 * args.micro_batch * cfg.seq_len * 8
+    comm_stats = None
+    if comm is not None:
+        st = comm.stats()
+        comm_stats = {"allreduce_calls": int(st.calls[1]), "in_switch_calls": int(st.nvls_calls), "kernel_launches": int(st.launches)}
+    algo_name = trainer.averager.algo
+    launch_mode = "CUDA graph replay" if trainer.use_graph else "eager"
+    gemm_counts = None
     if rank == 0:
         from piccl_b200.ops import gemm
+        gemm_counts = gemm.counts()
+    # the training job leaves the GPUs before rank 0 starts the child jobs of the other sections
+    if world > 1:
+        dist.barrier()
+        comm.close()
+        dist.destroy_process_group()
+    del trainer, dev
+    torch.cuda.empty_cache()
+    if rank == 0:
         line = {
             "metric": "DDP GPT-2 medium training throughput" if args.model == "medium" else "DDP GPT-2 tiny training throughput",
             "value": round(tokens_per_step / ms_dev * 1e3, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -178,20 +286,20 @@ def run_piccl(args):
             "data": "synthetic: token ids uniform over the vocabulary, random-init weights", "impl": "piccl_b200",
             "config": {"model": f"gpt2-{args.model}", "layers": cfg.n_layer, "d_model": cfg.d_model, "heads": cfg.n_head, "vocab": cfg.vocab_size,
                        "global_batch": world * args.micro_batch, "micro_batch_per_gpu": args.micro_batch, "seq_len": cfg.seq_len,
-                       "parallelism": f"dp{world}", "bucket_mb": 25, "allreduce_algo": trainer.averager.algo, "optimizer": "AdamW (in timed region)",
+                       "parallelism": f"dp{world}", "bucket_mb": 25, "allreduce_algo": algo_name, "optimizer": "AdamW (in timed region)", "launch_mode": launch_mode,
                        "l2": "working set per step (>= 7 GB of weights, activations and gradients) is far larger than the 126 MB L2; no explicit flush",
-                       "gemm_calls": gemm.counts()},
+                       "gemm_calls": gemm_counts, "communicator": comm_stats},
             "e2e": {"value": round(tokens_per_step / ms_e2e * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 3), "wall_ms_per_step": round(wall_e2e, 3),
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "api": "piccl_b200.train.DataParallelTrainer.step", "last_loss": last_loss},
             "gpu_launches": int(launches), "clocks": clocks,
         }
-        if coll:
-            line["collectives"] = coll
+        if world > 1:
+            time.sleep(2.0)                               # the other ranks' processes end and free their memory
+            if not args.no_dropin:
+                line["dropin"] = run_dropin(args, world)
+            if not args.no_collectives:
+                line["collectives"] = run_collectives(world)
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        comm.close()
-        dist.destroy_process_group()
     return 0
 
 
@@ -321,9 +429,20 @@ def run_reference(args):
     ms_dev, _, _ = timed_region(step_dev, args.steps, args.warmup, world)
     ms_e2e, wall_e2e, last_loss = timed_region(step_e2e, args.steps, max(1, args.warmup // 2), world)
     clocks = sampler.stop() if sampler else None
+    shim = None
+    if args.impl == "ddp" and os.environ.get("LD_PRELOAD"):
+        # calls the preloaded interposer ran itself / handed to NCCL, per collective (all-gather, all-reduce, broadcast, reduce, reduce-scatter)
+        try:
+            import ctypes
+            lib = ctypes.CDLL(os.environ["LD_PRELOAD"])
+            nat, pas = (ctypes.c_ulonglong * 5)(), (ctypes.c_ulonglong * 5)()
+            lib.piccl_shim_counters(nat, pas)
+            shim = {"fused": list(nat), "passed_to_nccl": list(pas), "order": ["allgather", "allreduce", "broadcast", "reduce", "reduce_scatter"]}
+        except (OSError, AttributeError):
+            shim = None
     if rank == 0:
         print(json.dumps({
-            "impl": os.environ.get("PICCL_BENCH_LABEL", "reference"), "metric": "DDP GPT-2 medium training throughput" if args.model == "medium" else "DDP GPT-2 tiny training throughput",
+            "impl": os.environ.get("PICCL_BENCH_LABEL", "reference"), "shim": shim, "metric": "DDP GPT-2 medium training throughput" if args.model == "medium" else "DDP GPT-2 tiny training throughput",
             "value": round(tokens_per_step / ms_dev * 1e3, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms_dev, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic: token ids uniform over the vocabulary, random-init weights",

@@ -12,11 +12,17 @@
 //   coll_bench --gpus 8 --coll allreduce --dtype float --min 8 --max 1073741824 --check
 //
 // Sizes: --min/--max are bytes of the whole buffer for allreduce/broadcast/reduce and bytes
-// per rank for allgather/reduce_scatter; powers of two in between (--step 4: every second one).
+// per rank for allgather/reduce_scatter; powers of two in between (--step 4: every second one),
+// or an explicit list with --sizes 8,4096,...
+// --algos RING,K_RING:2,PRM:4,AUTO runs the size list once per entry inside the same processes: before each
+// pass every rank sets PICCL_<COLL>_ALGO / _K and asks the preloaded library to read its environment again
+// (piccl_env_reload, found with dlsym; without this framework's library preloaded the flag is refused).
+// Rows are labelled <label>-<ALGO>-k<K>.
 // Output: one CSV line per size on stdout (rank 0).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <dlfcn.h>
 #include <nccl.h>
 #include <signal.h>
 #include <sys/mman.h>
@@ -28,6 +34,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <string>
+#include <utility>
 #include <vector>
 
 #define CK(x) do { cudaError_t e_ = (x); if (e_ != cudaSuccess) { fprintf(stderr, "rank %d: %s: %s\n", g_rank, #x, cudaGetErrorString(e_)); _exit(10); } } while (0)
@@ -61,6 +68,8 @@ struct Opt {
   int gpus = 2; CollKind coll = AR; std::string coll_name = "allreduce"; ncclDataType_t dt = ncclFloat; std::string dt_name = "float";
   ncclRedOp_t op = ncclSum; std::string op_name = "sum"; size_t minb = 8, maxb = 1 << 26; int root = 0; bool check = false, in_place = false;
   int iters_small = 1000, iters_large = 100, warmup = 5, step = 2; size_t large = 1000000; std::string label = "";
+  std::vector<size_t> sizes;                                  // --sizes: explicit list instead of min/max/step
+  std::vector<std::pair<std::string, int>> algos;             // --algos: (algorithm, k) passes inside one process
 };
 
 static size_t dt_size(ncclDataType_t d) { switch (d) { case ncclFloat: return 4; case ncclInt32: return 4; case ncclBfloat16: return 2; case ncclHalf: return 2; case ncclDouble: return 8; default: return 1; } }
@@ -122,14 +131,33 @@ static int run_rank(const Opt& o, int rank, Shared* sh) {
   cudaEvent_t e0, e1; CK(cudaEventCreate(&e0)); CK(cudaEventCreate(&e1));
   size_t es = dt_size(o.dt);
   bool per_rank = (o.coll == AG || o.coll == RS);
-  size_t max_count = o.maxb / es;
+  size_t maxb = o.maxb;
+  if (!o.sizes.empty()) { maxb = 0; for (size_t b : o.sizes) maxb = b > maxb ? b : maxb; }
+  size_t max_count = maxb / es; if (max_count == 0) max_count = 1;
   size_t big = per_rank ? max_count * n : max_count;
   char *sbuf, *rbuf;
   CK(cudaMalloc(&sbuf, big * es + 256)); CK(cudaMalloc(&rbuf, big * es + 256));
   CK(cudaMemset(sbuf, 0, big * es)); CK(cudaMemset(rbuf, 0, big * es));
   if (rank == 0) printf("# coll,label,dtype,op,ranks,bytes,iters,time_us,algbw_GBs,busbw_GBs,check\n");
-
-  for (size_t bytes = o.minb; bytes <= o.maxb; bytes *= o.step) {
+  std::vector<size_t> sizes = o.sizes;
+  if (sizes.empty()) for (size_t b = o.minb; b <= o.maxb; b *= o.step) sizes.push_back(b);
+  typedef void (*ReloadFn)(void);
+  ReloadFn reload = o.algos.empty() ? nullptr : (ReloadFn)dlsym(RTLD_DEFAULT, "piccl_env_reload");
+  if (!o.algos.empty() && !reload) { fprintf(stderr, "rank %d: --algos needs this framework's library preloaded (piccl_env_reload not found)\n", rank); _exit(13); }
+  const size_t passes = o.algos.empty() ? 1 : o.algos.size();
+  for (size_t pass = 0; pass < passes; pass++) {
+  std::string label = o.label;
+  if (!o.algos.empty()) {
+    std::string up = o.coll_name; for (auto& ch : up) ch = (char)toupper(ch);
+    CK(cudaStreamSynchronize(st));
+    host_barrier(sh, n, &sense);                              // nobody switches while a peer is still inside a collective of the last pass
+    setenv(("PICCL_" + up + "_ALGO").c_str(), o.algos[pass].first.c_str(), 1);
+    setenv(("PICCL_" + up + "_K").c_str(), std::to_string(o.algos[pass].second).c_str(), 1);
+    reload();
+    host_barrier(sh, n, &sense);
+    label += (label.empty() ? "" : "-") + o.algos[pass].first + "-k" + std::to_string(o.algos[pass].second);
+  }
+  for (size_t bytes : sizes) {
     size_t count = bytes / es; if (count == 0) count = 1;
     size_t send_count = (o.coll == RS) ? count * n : count, recv_count = (o.coll == AG) ? count * n : count;
     const void* send = sbuf; void* recv = rbuf;
@@ -190,11 +218,12 @@ static int run_rank(const Opt& o, int rank, Shared* sh) {
       double total = per_rank ? (double)count * es * n : (double)count * es;
       double algbw = total / us / 1e3;
       double factor = o.coll == AR ? 2.0 * (n - 1) / n : per_rank ? (double)(n - 1) / n : 1.0;
-      printf("%s,%s,%s,%s,%d,%zu,%d,%.3f,%.3f,%.3f,%s\n", o.coll_name.c_str(), o.label.c_str(), o.dt_name.c_str(), o.op_name.c_str(), n, count * es, iters, us, algbw,
+      printf("%s,%s,%s,%s,%d,%zu,%d,%.3f,%.3f,%.3f,%s\n", o.coll_name.c_str(), label.c_str(), o.dt_name.c_str(), o.op_name.c_str(), n, count * es, iters, us, algbw,
              algbw * factor, check < 0 ? "-" : check ? "ok" : "FAIL");
       fflush(stdout);
     }
     host_barrier(sh, n, &sense);
+  }
   }
   CK(cudaStreamSynchronize(st));
   NK(ncclCommDestroy(comm));
@@ -221,6 +250,8 @@ int main(int argc, char** argv) {
     else if (f == "--warmup") o.warmup = atoi(val().c_str());
     else if (f == "--label") o.label = val();
     else if (f == "--step") { o.step = atoi(val().c_str()); if (o.step < 2) o.step = 2; }
+    else if (f == "--sizes") { std::string v = val(); size_t p = 0; while (p < v.size()) { size_t q = v.find(',', p); if (q == std::string::npos) q = v.size(); if (q > p) o.sizes.push_back(strtoull(v.substr(p, q - p).c_str(), nullptr, 10)); p = q + 1; } }
+    else if (f == "--algos") { std::string v = val(); size_t p = 0; while (p < v.size()) { size_t q = v.find(',', p); if (q == std::string::npos) q = v.size(); std::string e = v.substr(p, q - p); size_t c = e.find(':'); if (!e.empty()) o.algos.push_back({e.substr(0, c), c == std::string::npos ? -1 : atoi(e.substr(c + 1).c_str())}); p = q + 1; } }
     else { fprintf(stderr, "unknown flag %s\n", f.c_str()); return 2; }
   }
   if (o.gpus < 1 || o.gpus > 64 || o.minb < 1 || o.maxb < o.minb) { fprintf(stderr, "bad arguments\n"); return 2; }

@@ -65,7 +65,7 @@ def targets() -> dict[str, dict]:
         },
         "coll_bench": {
             "src": [ROOT / "benchmarks" / "coll_bench.cc"],
-            "link": ["-cudart", "static", "-ldl", "-lpthread", "-lrt", "-L/usr/lib/x86_64-linux-gnu", "-lnccl"],
+            "link": ["-cudart", "static", "-ldl", "-lpthread", "-lrt", "-L/usr/lib/x86_64-linux-gnu", "-lnccl", "-Xcompiler", "-rdynamic"],
         },
     }
 

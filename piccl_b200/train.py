@@ -36,10 +36,10 @@ class DataParallelTrainer:
         self._tgt = None
         # CUDA graph of the whole step (forward, backward with overlapped bucket reductions, AdamW): after two eager steps
         # the launches are captured once and replayed, which removes the per-launch host cost (about a thousand launches).
-        # Default: on for a single GPU; with several ranks only on request (PICCL_TRAIN_GRAPH=1), the eager path is the
-        # one that was measured on 2, 4 and 8 GPUs.
+        # Off unless asked for (PICCL_TRAIN_GRAPH=1 or use_graph=True), on one GPU and on several alike, so that step times at
+        # different GPU counts compare the same launch mode.
         env_graph = os.environ.get("PICCL_TRAIN_GRAPH")
-        default_graph = (env_graph == "1") if env_graph is not None else (comm is None or comm.nranks == 1)
+        default_graph = env_graph == "1"
         self.use_graph = default_graph if use_graph is None else use_graph
         self._graph = None
         self._graph_loss = None

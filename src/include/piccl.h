@@ -81,6 +81,8 @@ int piccl_select_algorithm(int nranks, int coll, unsigned long long bytes, int* 
 int piccl_select_algorithm_ex(int nranks, int coll, unsigned long long bytes, int have_window, int* k);
 /* The configuration in force as "key=value" pairs; returns the length needed, like snprintf. */
 int piccl_env_describe(char* buf, int len);
+/* Reads the PICCL_* environment again; call it on every rank at the same point between collectives. */
+void piccl_env_reload(void);
 int piccl_comm_rank(piccl_comm_t* c);
 int piccl_comm_nranks(piccl_comm_t* c);
 const char* piccl_last_error(void);                         /* thread-local text of the last failure */

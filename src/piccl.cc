@@ -16,8 +16,16 @@
 //  * return codes are real; collectives inside an application ncclGroupStart/End pair,
 //    during stream capture before the communicator is set up, with custom reduction
 //    operators or unsupported types go to the real NCCL.
+//  * the set-up of a communicator is itself a collective (handles travel over the real
+//    NCCL), so whether and when it runs depends only on what is the same on every rank:
+//    it is started by the first intercepted collective of ANY kind, count and type
+//    outside a group and outside a stream capture, as soon as any algorithm variable is
+//    set; whether that very call then runs here or in NCCL is decided afterwards.
+//  * ncclCommFinalize / Split / Shrink / InitRankConfig / InitAll are hooked so that the registry never
+//    keeps state for a communicator handle that NCCL has given away again.
 #include <cuda_runtime.h>
 #include <dlfcn.h>
+#include <atomic>
 #include <nccl.h>
 #include <cstdio>
 #include <cstdlib>
@@ -62,7 +70,7 @@ struct ShimComm {
 std::mutex g_mu;
 std::map<ncclComm_t, ShimComm*> g_comms;
 thread_local int g_group_depth = 0;
-unsigned long long g_passthrough[COLL_COUNT], g_native[COLL_COUNT];
+std::atomic<unsigned long long> g_passthrough[COLL_COUNT], g_native[COLL_COUNT];
 
 ShimComm* shim_of(ncclComm_t comm) {
   std::lock_guard<std::mutex> l(g_mu);
@@ -126,28 +134,46 @@ bool bootstrap(ShimComm* s, ncclComm_t comm) {
   return ok;
 }
 
+bool any_algorithm_set() {
+  const Env& e = env();
+  for (int c = 0; c < COLL_COUNT; c++) if (e.algo[c] != ALGO_DEFAULT_NCCL) return true;
+  return false;
+}
+
 // Decides whether this call runs natively; sets up the communicator on first use.
 piccl_comm_t* native_comm(Coll coll, ncclComm_t comm, cudaStream_t stream, size_t count, ncclDataType_t dt, int op, Algo* algo, int* k) {
   const Env& e = env();
   *algo = e.algo[coll]; *k = e.k[coll];
-  if (*algo == ALGO_DEFAULT_NCCL) return nullptr;                       // the reference's default path
-  if (g_group_depth > 0 || count == 0) return nullptr;
+  if (!any_algorithm_set()) return nullptr;                             // the reference's default path: nothing is ever set up
+  if (g_group_depth > 0) return nullptr;
+  ShimComm* s = shim_of(comm);
+  std::lock_guard<std::mutex> l(s->mu);
+  if (!s->tried) {
+    // Every rank reaches this point with the same call of the same communicator, whatever the call's count, type or operator.
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    cudaError_t ce = cudaStreamIsCapturing(stream, &cs);
+    if (ce != cudaSuccess) {
+      cudaGetLastError();
+      s->tried = true; s->usable = false;
+      log_msg(1, "communicator %p: no usable CUDA device (%s) at the first intercepted call (%s, count %zu): NCCL is used", (void*)comm, cudaGetErrorString(ce), coll_name(coll), count);
+      return nullptr;
+    }
+    if (cs != cudaStreamCaptureStatusNone) return nullptr;              // set up at the first call outside a capture
+    s->tried = true;
+    s->usable = bootstrap(s, comm);
+    log_msg(1, "communicator %p rank %d/%d: %s (set up at the first intercepted call: %s, count %zu)", (void*)comm, s->rank, s->nranks,
+            s->usable ? "fused executor ready" : "using NCCL", coll_name(coll), count);
+  }
+  if (!s->usable) return nullptr;
+  // what this particular call needs
+  if (*algo == ALGO_DEFAULT_NCCL || count == 0) return nullptr;
   if (!dtype_size((int)dt)) return nullptr;                              // fp8 and future types
   const bool reducing = coll == COLL_ALLREDUCE || coll == COLL_REDUCE || coll == COLL_REDUCE_SCATTER;
   if (reducing) {
     if (op < 0 || op > 4) return nullptr;                                // ncclRedOpCreatePreMulSum handles
     if (op == 4 && !(dt == ncclFloat32 || dt == ncclFloat16 || dt == ncclBfloat16 || dt == ncclFloat64)) return nullptr;
   }
-  ShimComm* s = shim_of(comm);
-  std::lock_guard<std::mutex> l(s->mu);
-  if (!s->tried) {
-    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
-    if (cudaStreamIsCapturing(stream, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) { cudaGetLastError(); return nullptr; }
-    s->tried = true;
-    s->usable = bootstrap(s, comm);
-    log_msg(1, "communicator %p rank %d/%d: %s", (void*)comm, s->rank, s->nranks, s->usable ? "fused executor ready" : "using NCCL");
-  }
-  return s->usable ? s->pc : nullptr;
+  return s->pc;
 }
 
 ncclResult_t to_nccl(int rc) {
@@ -173,7 +199,7 @@ __attribute__((constructor)) void piccl_loaded() {
 __attribute__((destructor)) void piccl_unloaded() {
   if (env().log_level >= 1)
     for (int c = 0; c < COLL_COUNT; c++)
-      if (g_native[c] || g_passthrough[c]) fprintf(stderr, "[PICCL %d] %s: %llu fused, %llu passed to NCCL\n", (int)getpid(), coll_name((Coll)c), g_native[c], g_passthrough[c]);
+      if (g_native[c] || g_passthrough[c]) fprintf(stderr, "[PICCL %d] %s: %llu fused, %llu passed to NCCL\n", (int)getpid(), coll_name((Coll)c), g_native[c].load(), g_passthrough[c].load());
 }
 
 }  // namespace
@@ -241,9 +267,49 @@ ncclResult_t ncclBcast(void* buff, size_t count, ncclDataType_t datatype, int ro
   return ncclBroadcast(buff, buff, count, datatype, root, comm, stream);
 }
 
+// Communicator creation: per-communicator state is made lazily, at the first collective.  A handle that NCCL hands out may be
+// the address of a communicator that was freed earlier without passing through a hook: whatever the registry still holds for
+// it belongs to that dead communicator and goes away.
 ncclResult_t ncclCommInitRank(ncclComm_t* comm, int nranks, ncclUniqueId commId, int rank) {
   REAL(ncclCommInitRank);
-  return real_ncclCommInitRank(comm, nranks, commId, rank);     // per-communicator state is made lazily
+  ncclResult_t rc = real_ncclCommInitRank(comm, nranks, commId, rank);
+  if (rc == ncclSuccess && comm && *comm) drop(*comm);
+  return rc;
+}
+
+ncclResult_t ncclCommInitRankConfig(ncclComm_t* comm, int nranks, ncclUniqueId commId, int rank, ncclConfig_t* config) {
+  REAL(ncclCommInitRankConfig);
+  ncclResult_t rc = real_ncclCommInitRankConfig(comm, nranks, commId, rank, config);
+  if ((rc == ncclSuccess || rc == ncclInProgress) && comm && *comm) drop(*comm);
+  return rc;
+}
+
+ncclResult_t ncclCommInitAll(ncclComm_t* comms, int ndev, const int* devlist) {
+  REAL(ncclCommInitAll);
+  ncclResult_t rc = real_ncclCommInitAll(comms, ndev, devlist);
+  if (rc == ncclSuccess && comms) for (int i = 0; i < ndev; i++) if (comms[i]) drop(comms[i]);
+  return rc;
+}
+
+ncclResult_t ncclCommSplit(ncclComm_t comm, int color, int key, ncclComm_t* newcomm, ncclConfig_t* config) {
+  REAL(ncclCommSplit);
+  ncclResult_t rc = real_ncclCommSplit(comm, color, key, newcomm, config);
+  if ((rc == ncclSuccess || rc == ncclInProgress) && newcomm && *newcomm) drop(*newcomm);
+  return rc;
+}
+
+ncclResult_t ncclCommShrink(ncclComm_t comm, int* excludeRanksList, int excludeRanksCount, ncclComm_t* newcomm, ncclConfig_t* config, int shrinkFlags) {
+  REAL(ncclCommShrink);
+  ncclResult_t rc = real_ncclCommShrink(comm, excludeRanksList, excludeRanksCount, newcomm, config, shrinkFlags);
+  if ((rc == ncclSuccess || rc == ncclInProgress) && newcomm && *newcomm) drop(*newcomm);
+  return rc;
+}
+
+// After ncclCommFinalize a communicator takes no more collectives: its heap and window go now, while the peers are still there.
+ncclResult_t ncclCommFinalize(ncclComm_t comm) {
+  drop(comm);
+  REAL(ncclCommFinalize);
+  return real_ncclCommFinalize(comm);
 }
 
 ncclResult_t ncclCommDestroy(ncclComm_t comm) {
@@ -285,7 +351,7 @@ ncclResult_t ncclGroupEnd() {
 
 // Counters of the shim itself (calls run by the fused executor / handed to NCCL).
 void piccl_shim_counters(unsigned long long* native, unsigned long long* passthrough) {
-  for (int c = 0; c < COLL_COUNT; c++) { if (native) native[c] = g_native[c]; if (passthrough) passthrough[c] = g_passthrough[c]; }
+  for (int c = 0; c < COLL_COUNT; c++) { if (native) native[c] = g_native[c].load(); if (passthrough) passthrough[c] = g_passthrough[c].load(); }
 }
 
 }  // extern "C"

@@ -94,6 +94,10 @@ void log_msg(int level, const char* fmt, ...) {
 
 }  // namespace piccl
 
+// Reads the PICCL_* environment again (benchmarks that switch the algorithm inside one process; all ranks must do it at the
+// same point between collectives).  Geometry that a communicator fixed at creation (heap, window) keeps its old values.
+extern "C" void piccl_env_reload(void) { piccl::env_reload(); }
+
 // The effective configuration as "key=value" pairs separated by blanks (for logs and tests).
 // Returns the length needed, like snprintf.
 extern "C" int piccl_env_describe(char* buf, int len) {

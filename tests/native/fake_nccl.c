@@ -18,6 +18,8 @@ int ncclBroadcast(const void* s, void* r, size_t c, int dt, int root, void* comm
 int ncclBcast(void* b, size_t c, int dt, int root, void* comm, void* st) { (void)b; (void)c; (void)dt; (void)root; (void)comm; (void)st; n_bc++; return 0; }
 int ncclCommInitRank(void** comm, int n, char id[128], int rank) { (void)n; (void)id; (void)rank; *comm = &fake_comm; n_init++; return 0; }
 int ncclCommDestroy(void* comm) { (void)comm; n_destroy++; return 0; }
+int ncclCommFinalize(void* comm) { (void)comm; return 0; }
+int ncclCommSplit(void* comm, int color, int key, void** newcomm, void* config) { (void)comm; (void)color; (void)key; (void)config; *newcomm = &fake_comm; n_init++; return 0; }
 int ncclCommAbort(void* comm) { (void)comm; return 0; }
 int ncclCommGetAsyncError(void* comm, int* err) { (void)comm; *err = 0; return 0; }
 int ncclCommCount(void* comm, int* n) { (void)comm; *n = ranks(); return 0; }

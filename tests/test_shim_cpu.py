@@ -186,3 +186,24 @@ def test_a_communicator_the_executor_cannot_serve_falls_back_without_breaking_th
         assert r.returncode == 0 and "collectives=0" in r.stdout, r.stdout + r.stderr
         assert "FAKE_NCCL allreduce=2 allgather=2 reduce_scatter=2 reduce=2 broadcast=2" in r.stdout
         assert "allreduce: 0 fused, 2 passed to NCCL" in r.stderr
+
+
+def test_the_set_up_is_decided_by_the_first_intercepted_call_whatever_its_count(tmp_path):
+    """The set-up of a communicator is a collective of its own, so every rank must start it at the same call: the first one
+    intercepted, even when this rank passes zero elements (which then goes to NCCL as before)."""
+    app = _fake_nccl_world(tmp_path)
+    r = _run_app(app, PICCL_ALLREDUCE_ALGO="RING", FAKE_NCCL_RANKS="4", NCCL_APP_ZERO_FIRST="1")
+    assert r.returncode == 0 and "collectives=0" in r.stdout, r.stdout + r.stderr
+    import re
+    assert re.search(r"first intercepted call:? \(?allgather, count 0", r.stderr), r.stderr
+    assert "FAKE_NCCL allreduce=2 allgather=3" in r.stdout          # the empty call itself still reached the library
+
+
+def test_a_handle_that_comes_back_from_a_split_gets_fresh_state(tmp_path):
+    """ncclCommFinalize drops what the interposer holds for a communicator; when a later ncclCommSplit hands out the same
+    address, the decision is made again for the new communicator instead of reusing the dead one's."""
+    app = _fake_nccl_world(tmp_path)
+    r = _run_app(app, PICCL_ALLREDUCE_ALGO="RING", FAKE_NCCL_RANKS="4", NCCL_APP_SPLIT="1")
+    assert r.returncode == 0 and "collectives=0" in r.stdout, r.stdout + r.stderr
+    assert r.stderr.count("first intercepted call") == 2, r.stderr
+    assert "FAKE_NCCL allreduce=3" in r.stdout
