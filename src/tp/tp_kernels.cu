@@ -96,7 +96,7 @@ struct RsPolicy {
     return reinterpret_cast<unsigned*>(R->heap[owner] + flag_off) + ((size_t)(parity * n + src) * tiles_per_owner + tid_);
   }
   __device__ bf16* inbox(int owner, int src, int tid_) const {
-    return reinterpret_cast<bf16*>(R->heap[owner] + data_off) + ((size_t)(parity * n + src) * tiles_per_owner + tid_) * (size_t)(GEMM_BM * TP_BN);
+    return reinterpret_cast<bf16*>(R->heap[owner] + data_off) + ((size_t)src * tiles_per_owner + tid_) * (size_t)(GEMM_BM * TP_BN);      // data_off: this call's half of the region
   }
   __device__ bool tile_begin(int m_blk, int n_blk, int et, volatile int* abort_flag) {
     if (m_blk / mb_per_owner != rank) return true;
@@ -178,7 +178,7 @@ struct AgPolicy {
   }
   __device__ const CUtensorMap* a_map(int m_blk, int& row0) const {
     if (m_blk / mb_per_shard == rank) { row0 = (m_blk % mb_per_shard) * GEMM_BM; return &R->ta; }
-    row0 = parity * M + m_blk * GEMM_BM; return &R->ta2;
+    row0 = m_blk * GEMM_BM; return &R->ta2;             // ta2 covers this call's half of the region
   }
   __device__ bool gate(int m_blk, volatile int* abort_flag) const {
     const int src = m_blk / mb_per_shard;
@@ -206,7 +206,7 @@ __device__ void ag_feed(const TpArgs& a, const TpRank* R, int feeder, int n_feed
     const int d = 1 + p / mbs, mb = p % mbs;             // distance-major: the peer that needs my shard next comes first
     const int dest = (rank - d + n) % n;
     const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(R->a_shard) + (size_t)mb * block_bytes);
-    uint4* dst = reinterpret_cast<uint4*>(R->heap[dest] + a.data_off + ((size_t)parity * a.M + (size_t)rank * (a.M / n) + (size_t)mb * GEMM_BM) * a.K * 2);
+    uint4* dst = reinterpret_cast<uint4*>(R->heap[dest] + a.data_off + ((size_t)rank * (a.M / n) + (size_t)mb * GEMM_BM) * a.K * 2);
     const size_t nvec = block_bytes / 16;
     size_t i = threadIdx.x;
     for (; i + 7 * GEMM_THREADS < nvec; i += 8 * GEMM_THREADS) {
@@ -235,6 +235,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) ag_gemm_kernel(const __grid_c
 }
 
 // ------------------------------------------------------------------ host
+// The workspace is used in four quarters: [kernel: gemm_rs, ag_gemm][parity of that kernel's call count].
+static long long tp_quarter(long long tp_bytes) { return tp_bytes / 4 / 1024 * 1024; }
+static long long tp_need_per_call(int which, int nranks, int M, int N, int K) {
+  if (which == 0) return (long long)nranks * ((long long)M / nranks / GEMM_BM) * (N / TP_BN) * (GEMM_BM * TP_BN * 2);     // [src][tile] bf16 tiles
+  return (long long)M * K * 2;                                                                                              // [M][K] bf16
+}
+
 static int tp_common_checks(piccl_comm** cs, int n, int M, int N, int K, int which) {
   if (n < 1 || n > TP_MAX_RANKS) return fail(PICCL_INVALID_ARGUMENT, "1..%d communicators per launch", TP_MAX_RANKS);
   piccl_comm* c = cs[0];
@@ -244,7 +251,7 @@ static int tp_common_checks(piccl_comm** cs, int n, int M, int N, int K, int whi
   const long long nflags = which == 0 ? 2LL * c->nranks * (M / c->nranks / GEMM_BM) * (N / TP_BN) : 2LL * c->nranks * (M / c->nranks / GEMM_BM);
   if (nflags * 4 > (512 << 10)) return fail(PICCL_UNSUPPORTED, "too many tiles for the flag area");
   long long need = piccl_tp_workspace_bytes(which, c->nranks, M, N, K);
-  if (c->h_ctx.tp_bytes < need) return fail(PICCL_INVALID_USAGE, "tensor-parallel workspace too small: %lld bytes needed, %lld configured (tp_bytes / PICCL_TP_MB)", need, c->h_ctx.tp_bytes);
+  if (tp_quarter(c->h_ctx.tp_bytes) < tp_need_per_call(which, c->nranks, M, N, K)) return fail(PICCL_INVALID_USAGE, "tensor-parallel workspace too small: %lld bytes needed, %lld configured (tp_bytes / PICCL_TP_MB)", need, c->h_ctx.tp_bytes);
   return PICCL_OK;
 }
 
@@ -256,7 +263,12 @@ static int tp_launch(piccl_comm** cs, int n, const void* const* A, const void* c
   TpArgs a; memset(&a, 0, sizeof a);
   a.n = nr; a.M = M; a.N = N; a.K = K;
   a.flag_off = c0->h_ctx.tp_flag_off + (which ? (512 << 10) : 0);   // the two kernels keep their flags apart
-  a.data_off = c0->h_ctx.tp_data_off;
+  // ... and their payload: each kernel owns one half of the workspace, and each call one half of that, chosen by the parity of
+  // the kernel's own call count.  The strides do not depend on the shape: a rank that is one call ahead (the other kernel, or
+  // the same kernel with another shape) never writes where a peer still reads the call before.
+  const long long quarter = tp_quarter(c0->h_ctx.tp_bytes);
+  const unsigned next_epoch = (which ? c0->tp_epoch_ag : c0->tp_epoch_rs) + 1;
+  a.data_off = c0->h_ctx.tp_data_off + (which ? 2 * quarter : 0) + (long long)(next_epoch & 1) * quarter;
   a.ctas_per_rank = std::max(1, c0->sm_count / n);
   a.n_feed = which ? std::min(std::max(1, env().tp_feeders), a.ctas_per_rank / 2) : 0;
   if (nr == 1) a.n_feed = 0;
@@ -274,7 +286,7 @@ static int tp_launch(piccl_comm** cs, int n, const void* const* A, const void* c
       a.epoch = ++c->tp_epoch_rs;
     } else {
       ok &= make_tmap_bf16_k64(&R.ta, A[i], (uint64_t)(M / nr), (uint64_t)K, (uint64_t)K, GEMM_BM);
-      ok &= make_tmap_bf16_k64(&R.ta2, c->heap + a.data_off, (uint64_t)2 * M, (uint64_t)K, (uint64_t)K, GEMM_BM);
+      ok &= make_tmap_bf16_k64(&R.ta2, c->heap + a.data_off, (uint64_t)M, (uint64_t)K, (uint64_t)K, GEMM_BM);
       a.epoch = ++c->tp_epoch_ag;
     }
     ok &= make_tmap_bf16_k64(&R.tb, B[i], (uint64_t)N, (uint64_t)K, (uint64_t)K, TP_BN);
@@ -302,8 +314,8 @@ using namespace piccl;
 extern "C" {
 
 long long piccl_tp_workspace_bytes(int which, int nranks, int M, int N, int K) {
-  if (which == 0) return 2LL * nranks * ((long long)M / nranks / GEMM_BM) * (N / TP_BN) * (GEMM_BM * TP_BN * 2);   // [parity][src][tile] bf16 tiles
-  return 2LL * M * K * 2;                                                                                            // [parity][M][K] bf16
+  // four quarters (two kernels x two calls in flight), each large enough for one call of this shape
+  return 4 * ((tp_need_per_call(which, nranks, M, N, K) + 1023) / 1024 * 1024);
 }
 int piccl_gemm_rs(piccl_comm_t* c, const void* A, const void* B, void* out, int M, int N, int K_local, void* stream) {
   if (!c) return fail(PICCL_INVALID_ARGUMENT, "null communicator");

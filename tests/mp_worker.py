@@ -190,6 +190,7 @@ def case_tp(rank, world):
     from piccl_b200.parallel import tp
     from piccl_b200.parallel.comm import Communicator, make_config
     M, N, K = 256 * world * 2, 1024, 512
+    M3, N3, K3 = 128 * world, 512, 256                          # a second, smaller GEMM -> reduce-scatter shape
     ws = max(tp.workspace_bytes("gemm_rs", world, M, N, K), tp.workspace_bytes("ag_gemm", world, M, N, K))
     comm = Communicator(config=make_config(tp_bytes=ws, timeout_ms=20000))
     g = torch.Generator(device="cuda").manual_seed(50 + rank)
@@ -217,6 +218,22 @@ def case_tp(rank, world):
     ref2 = full @ B.t()
     tol = 0.03 * ref2.float().abs().max().item() + 0.05
     assert torch.allclose(out2.float(), ref2.float(), atol=tol, rtol=3e-2), (out2.float() - ref2.float()).abs().max().item()
+    # the two kernels and two shapes alternating on one stream with no host synchronisation in between
+    A3 = torch.randn(M3, K3, generator=g, device="cuda").to(torch.bfloat16)
+    B3 = (torch.randn(N3, K3, generator=g, device="cuda") * 0.1).to(torch.bfloat16)
+    out3 = torch.empty(M3 // world, N3, device="cuda", dtype=torch.bfloat16)
+    out.fill_(float("nan")); out2.fill_(float("nan"))
+    for _ in range(5):
+        tp.ag_gemm(comm, As, B, out2)
+        tp.gemm_rs(comm, A, B, out)
+        tp.gemm_rs(comm, A3, B3, out3)
+    torch.cuda.synchronize()
+    assert tp.tp_status(comm) == 0
+    ref3 = torch.empty_like(out3)
+    dist.reduce_scatter_tensor(ref3, A3 @ B3.t())
+    assert torch.allclose(out.float(), ref.float(), atol=0.03 * ref.float().abs().max().item() + 0.05, rtol=3e-2)
+    assert torch.allclose(out2.float(), ref2.float(), atol=0.03 * ref2.float().abs().max().item() + 0.05, rtol=3e-2)
+    assert torch.allclose(out3.float(), ref3.float(), atol=0.03 * ref3.float().abs().max().item() + 0.05, rtol=3e-2)
     dist.barrier()
     comm.close()
 
