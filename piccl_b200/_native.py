@@ -20,7 +20,7 @@ DTYPE = {"int8": 0, "uint8": 1, "int32": 2, "uint32": 3, "int64": 4, "uint64": 5
 
 class Config(C.Structure):
     _fields_ = [("max_cta", C.c_int), ("nslot", C.c_int), ("slot_bytes", C.c_longlong), ("scratch_bytes", C.c_longlong),
-                ("block_size", C.c_int), ("timeout_ms", C.c_int), ("tp_bytes", C.c_longlong)]
+                ("block_size", C.c_int), ("timeout_ms", C.c_int), ("tp_bytes", C.c_longlong), ("nvls_cta", C.c_int)]
 
 
 class Handle(C.Structure):

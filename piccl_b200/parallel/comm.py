@@ -40,8 +40,10 @@ def _algo(algo) -> int:
     return algo if isinstance(algo, int) else N.ALGO[algo.upper()]
 
 
-def make_config(max_cta=0, nslot=0, slot_bytes=0, scratch_bytes=0, block_size=0, timeout_ms=0, tp_bytes=0) -> N.Config:
-    return N.Config(max_cta, nslot, slot_bytes, scratch_bytes, block_size, timeout_ms, tp_bytes)
+def make_config(max_cta=0, nslot=0, slot_bytes=0, scratch_bytes=0, block_size=0, timeout_ms=0, tp_bytes=0, nvls_cta=0) -> N.Config:
+    """0 everywhere: the library's defaults / PICCL_* environment.  nvls_cta: CTAs of the in-switch collectives (the default, 128,
+    is for stand-alone bandwidth; 48 leaves room for a backward pass that runs at the same time)."""
+    return N.Config(max_cta, nslot, slot_bytes, scratch_bytes, block_size, timeout_ms, tp_bytes, nvls_cta)
 
 
 class _CommBase:

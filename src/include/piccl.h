@@ -38,6 +38,8 @@ typedef struct {
   int block_size;         /* threads per CTA; 0: PICCL_BLOCK_SIZE or 512 */
   int timeout_ms;         /* bound of every device-side wait; 0: PICCL_TIMEOUT_MS or 10000 */
   long long tp_bytes;     /* workspace of the fused tensor-parallel kernels; 0: PICCL_TP_MB (default none) */
+  int nvls_cta;           /* CTAs (slots of the multicast window) of the in-switch collectives; 0: PICCL_NVLS_CTA or 128.  Fewer CTAs leave
+                             more SMs to kernels that run at the same time (48 suits gradient buckets overlapped with a backward pass) */
 } piccl_config_t;
 
 typedef struct piccl_comm piccl_comm_t;

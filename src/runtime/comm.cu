@@ -79,6 +79,7 @@ int piccl_comm_create(int rank, int nranks, int device, const piccl_config_t* us
   cfg.block_size = cfg.block_size / 32 * 32;
   if (cfg.timeout_ms <= 0) cfg.timeout_ms = e.timeout_ms;
   if (cfg.max_cta > 128) cfg.max_cta = 128;
+  if (cfg.nvls_cta <= 0) cfg.nvls_cta = e.nvls_cta;
 
   DevGuard g(device);
   piccl_comm* c = new piccl_comm();
@@ -142,6 +143,7 @@ int piccl_comm_local_handle(piccl_comm_t* c, piccl_handle_t* out) {
   cudaError_t e = cudaIpcGetMemHandle(&b.ipc, c->heap);
   b.ipc_ok = (e == cudaSuccess) ? 1 : 0;
   if (env().nvls && nvls_device_capable(c->device)) b.ipc_ok |= 2;
+  b.ipc_ok |= (c->cfg.nvls_cta & 0xff) << 8;                 // the window geometry must agree on all ranks
   if (e != cudaSuccess) { cudaGetLastError(); log_msg(1, "cudaIpcGetMemHandle: %s (peers in other processes cannot map this rank)", cudaGetErrorString(e)); }
   static_assert(sizeof(HandleBlob) <= sizeof(piccl_handle_t), "handle blob too large");
   memset(out, 0, sizeof *out); memcpy(out->bytes, &b, sizeof b);
@@ -157,6 +159,7 @@ int piccl_comm_connect(piccl_comm_t* c, const piccl_handle_t* all) {
     if (b.magic != kHandleMagic || b.rank != p || b.nranks != c->nranks) return fail(PICCL_INVALID_ARGUMENT, "handle %d is not a handle of rank %d of this communicator", p, p);
     if (b.max_cta != c->cfg.max_cta || b.nslot != c->cfg.nslot || (long long)b.slot_bytes != c->cfg.slot_bytes || (long long)b.heap_bytes != c->heap_bytes)
       return fail(PICCL_INVALID_USAGE, "rank %d uses a different heap layout (PICCL_MAX_CTA/NSLOT/SLOT_KB/SCRATCH_MB must agree)", p);
+    if (((b.ipc_ok >> 8) & 0xff) != (c->cfg.nvls_cta & 0xff)) return fail(PICCL_INVALID_USAGE, "rank %d uses a different number of in-switch CTAs (nvls_cta / PICCL_NVLS_CTA must agree)", p);
     if (p == c->rank) { c->h_ctx.heap[p] = c->heap; continue; }
     if (b.host_id != c->host_id) return fail(PICCL_UNSUPPORTED, "rank %d is on another host: peer memory is not reachable", p);
     if (b.pid == (int)getpid()) {

@@ -15,7 +15,7 @@ namespace piccl {
 constexpr unsigned kHandleMagic = 0x5049434cu;   // "PICL"
 
 struct HandleBlob {
-  unsigned magic; int rank, nranks, pid, device; int max_cta, nslot, ipc_ok;   // ipc_ok bit 0: heap exported; bit 1: wants and can use an NVLink multicast window
+  unsigned magic; int rank, nranks, pid, device; int max_cta, nslot, ipc_ok;   // ipc_ok bit 0: heap exported; bit 1: wants and can use an NVLink multicast window; bits 8-15: CTAs of the in-switch collectives
   unsigned long long host_id, heap_bytes, raw_ptr, slot_bytes;
   cudaIpcMemHandle_t ipc;
 };

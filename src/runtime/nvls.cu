@@ -131,9 +131,9 @@ bool nvls_device_capable(int device) {
 bool nvls_ready(const piccl_comm* c) { return c->nvls && static_cast<const NvlsState*>(c->nvls)->ready; }
 bool nvls_emulated(const piccl_comm* c) { return nvls_ready(c) && static_cast<const NvlsState*>(c->nvls)->emulated; }
 
-static void window_geometry(NvlsState* s, bool emulated) {
+static void window_geometry(const piccl_comm* c, NvlsState* s, bool emulated) {
   const Env& e = env();
-  s->max_cta = std::max(1, std::min(e.nvls_cta, emulated ? 32 : kNvlsMaxCta));
+  s->max_cta = std::max(1, std::min(c->cfg.nvls_cta > 0 ? c->cfg.nvls_cta : e.nvls_cta, emulated ? 32 : kNvlsMaxCta));
   s->depth = std::max(2, std::min(e.nvls_depth, kNvlsMaxDepth));
   const long long part = (std::max<long long>(1, e.nvls_chunk_kb) * 1024 + 255) / 256 * 256;     // one part = one chunk of at most PICCL_NVLS_CHUNK_KB
   s->slot_bytes = s->depth * part;
@@ -143,7 +143,7 @@ static void window_geometry(NvlsState* s, bool emulated) {
 void nvls_setup_emulated(piccl_comm* c) {
   NvlsState* s = new NvlsState();
   c->nvls = s;
-  window_geometry(s, true);
+  window_geometry(c, s, true);
   s->emulated = true;
   s->win = (size_t)kNvlsFlagBytes + (size_t)s->max_cta * (size_t)s->slot_bytes;
   cudaError_t ce = cudaMalloc(&s->emu_win, s->win);
@@ -212,7 +212,7 @@ void nvls_setup(piccl_comm* c, int root_pid, unsigned long long root_id) {
   STEP(d.CtxGetDevice(&s->dev));
 
   // window geometry: the same arithmetic on every rank
-  window_geometry(s, false);
+  window_geometry(c, s, false);
   size_t want = (size_t)kNvlsFlagBytes + (size_t)s->max_cta * (size_t)s->slot_bytes;
   CUmulticastObjectProp mp; memset(&mp, 0, sizeof mp);
   mp.numDevices = (unsigned)n; mp.size = want; mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
