@@ -149,7 +149,7 @@ def run_dropin(args, world: int):
             except ValueError:
                 continue
             keep = {"value": d.get("value"), "unit": d.get("unit"), "ms_per_step": d.get("ms_per_step"), "e2e": d.get("e2e"), "shim": d.get("shim"),
-                    "stack": "torch DistributedDataParallel + fused AdamW on benchmarks/torch_gpt2.py, LD_PRELOAD=piccl.so", "allreduce_algo_env": algo}
+                    "stack": "torch DistributedDataParallel + fused AdamW on benchmarks/torch_gpt2.py, LD_PRELOAD=piccl.so", "allreduce_algo_env": algo, "nvls_cta_env": os.environ.get("PICCL_NVLS_CTA", "48")}
             return keep
     return {"unavailable": f"rc {r.returncode}: " + (r.stderr.strip().splitlines() or ["no output"])[-1][:200]}
 

@@ -4,10 +4,13 @@
     python benchmarks/profile_cases.py exec_ll   # low-latency all-reduce, 8 virtual ranks, 16 KiB
     python benchmarks/profile_cases.py gemm      # tcgen05 GEMM 8192 x 8192 x 3584 bf16
     python benchmarks/profile_cases.py gemm_pair # the same product on CTA pairs (tcgen05.mma.cta_group::2); checks the result first
-    python benchmarks/profile_cases.py direct    # DIRECT all-reduce, 8 virtual ranks, 16 MiB fp32 (add PICCL_EXEC_DEFER=1 for lazy counters)
+    python benchmarks/profile_cases.py direct    # DIRECT all-reduce, 8 virtual ranks, 16 MiB fp32
     python benchmarks/profile_cases.py tp        # fused GEMM -> reduce-scatter, 2 virtual ranks, 4096 x 4096 x 2048
     python benchmarks/profile_cases.py ln        # residual-add + LayerNorm forward/backward, 8192 x 1024
     python benchmarks/profile_cases.py ce        # cross entropy forward+backward, 8192 x 50304
+    python benchmarks/profile_cases.py nvls      # in-switch all-reduce kernel with the switch emulated: 4 virtual ranks, 64 MiB bf16 each
+    python benchmarks/profile_cases.py llf       # low-latency executor: all-gather of 16 KiB per rank, 8 virtual ranks
+    python benchmarks/profile_cases.py ag_gemm   # fused all-gather -> GEMM, 2 virtual ranks, 4096 x 2048 x 4096
 
 Typical capture (after the same command has exited 0 without ncu):
     ncu --set full --clock-control none -k regex:<kernel> -s 2 -c 2 -o <name> python benchmarks/profile_cases.py <case>
@@ -89,6 +92,49 @@ def case_tp():
     g.close()
 
 
+def case_nvls():
+    """The kernel of the in-switch collectives on one GPU: the multimem instructions are replaced by loops over the virtual
+    ranks' windows, everything else (bulk copies, warp groups, counters) is what runs on NVLink multicast windows."""
+    from piccl_b200.parallel.comm import LoopbackGroup
+    n, count = 4, 32 << 20
+    g = LoopbackGroup(n)
+    xs = [torch.ones(count, device="cuda", dtype=torch.bfloat16) for _ in range(n)]
+    outs = [torch.empty_like(x) for x in xs]
+    for _ in range(3):
+        g.run("allreduce", xs, outs, count, algo="NVLS")
+    torch.cuda.synchronize()
+    assert g.status().aborted == 0 and g.stats().nvls_calls == 3 and float(outs[1][777]) == float(n)
+    g.close()
+
+
+def case_llf():
+    from piccl_b200.parallel.comm import LoopbackGroup
+    n, count = 8, 4096
+    g = LoopbackGroup(n)
+    xs = [torch.full((count,), float(r), device="cuda") for r in range(n)]
+    outs = [torch.empty(n * count, device="cuda") for _ in range(n)]
+    for _ in range(4):
+        g.run("allgather", xs, outs, count, algo="RING")
+    torch.cuda.synchronize()
+    assert g.status().aborted == 0 and float(outs[2][5 * count + 1]) == 5.0
+    g.close()
+
+
+def case_ag_gemm():
+    from piccl_b200.parallel import tp
+    from piccl_b200.parallel.comm import LoopbackGroup, make_config
+    n, M, N, K = 2, 4096, 2048, 4096
+    g = LoopbackGroup(n, config=make_config(tp_bytes=tp.workspace_bytes("ag_gemm", n, M, N, K)))
+    As = [torch.randn(M // n, K, device="cuda").to(torch.bfloat16) for _ in range(n)]
+    Bs = [torch.randn(N, K, device="cuda").to(torch.bfloat16) for _ in range(n)]
+    outs = [torch.empty(M, N, device="cuda", dtype=torch.bfloat16) for _ in range(n)]
+    for _ in range(4):
+        tp.ag_gemm_group(g, As, Bs, outs)
+    torch.cuda.synchronize()
+    assert all(tp.tp_status(h) == 0 for h in g._hs)
+    g.close()
+
+
 def case_ln():
     from piccl_b200 import ops
     T, C = 8192 * 4, 1024
@@ -116,5 +162,5 @@ def case_ce():
 
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "exec"
-    {"exec": case_exec, "exec_ll": lambda: case_exec(True), "gemm": case_gemm, "gemm_pair": case_gemm_pair, "direct": case_direct, "tp": case_tp, "ln": case_ln, "ce": case_ce}[which]()
+    {"exec": case_exec, "exec_ll": lambda: case_exec(True), "gemm": case_gemm, "gemm_pair": case_gemm_pair, "direct": case_direct, "tp": case_tp, "ln": case_ln, "ce": case_ce, "nvls": case_nvls, "llf": case_llf, "ag_gemm": case_ag_gemm}[which]()
     print(f"profile case {which} done")
