@@ -76,6 +76,19 @@ struct LLArgs {
   LLRank r[kMaxVRanks];
 };
 typedef void (*LLKernelFn)(LLArgs);
+// ---- low-latency all-gather / reduce-scatter: one exchange with every rank (ll_exchange.cu)
+struct LLXArgs {
+  int n_vrank, n_cta, avg;
+  float scale;
+  unsigned epoch;
+  unsigned long long timeout_ns;
+  long long count;                        // all-gather: BYTES per rank; reduce-scatter: elements per rank
+  LLRank r[kMaxVRanks];
+};
+typedef void (*LLXKernelFn)(LLXArgs);
+LLXKernelFn llx_allgather_kernel();
+LLXKernelFn llx_reduce_scatter_kernel_for(int dtype, int op);
+int llx_lines_per_cta();
 LLKernelFn ll_kernel_for(int dtype, int op);
 int ll_lines_per_cta();
 

@@ -465,6 +465,40 @@ static int run(piccl_comm** comms, int n, const CallDesc* calls, cudaStream_t st
     }
   }
 
+  // small all-gather / reduce-scatter whose schedule is one exchange with every rank (DIRECT, or RM / PRM with a radix of at least
+  // the rank count): the low-latency exchange kernel.  (Not while capturing: the epoch is a launch argument.)
+  if (cap_state == cudaStreamCaptureStatusNone && (d0.coll == COLL_ALLGATHER || d0.coll == COLL_REDUCE_SCATTER) && c0->ll_max_bytes > 0 && c0->nranks >= 2 &&
+      (long long)d0.count * esz_real <= std::min<long long>(c0->ll_max_bytes, (long long)env().llx_kb * 1024) &&
+      (d0.algo == ALGO_DIRECT || ((d0.algo == ALGO_RM || d0.algo == ALGO_PRM) && d0.k >= c0->nranks))) {
+    LLXKernelFn xf = d0.coll == COLL_ALLGATHER ? llx_allgather_kernel() : llx_reduce_scatter_kernel_for(d0.dtype, op);
+    LLXArgs xa; memset(&xa, 0, sizeof xa);
+    xa.n_vrank = n; xa.avg = avg ? 1 : 0; xa.scale = avg ? 1.0f / (float)c0->nranks : 1.0f;
+    xa.count = d0.coll == COLL_ALLGATHER ? (long long)d0.count * esz_real : (long long)d0.count;
+    xa.timeout_ns = (unsigned long long)c0->cfg.timeout_ms * 1000000ull;
+    const long long nlines = d0.coll == COLL_ALLGATHER ? (xa.count + 7) / 8 : ((long long)d0.count + (8 / esz_real) - 1) / (8 / esz_real);
+    xa.n_cta = (int)((nlines + llx_lines_per_cta() - 1) / llx_lines_per_cta());
+    if (xf && esz_real <= 8 && n * xa.n_cta <= c0->sm_count) {
+      bool skip = false;
+      for (int i = 0; i < n; i++) {
+        piccl_comm* c = comms[i];
+        std::lock_guard<std::mutex> l(c->mu);
+        xa.r[i].ctx = c->d_ctx; xa.r[i].in = calls[i].send; xa.r[i].out = calls[i].recv;
+        xa.epoch = ++c->ll_epoch;
+        c->stats.launches++; c->stats.calls[d0.coll]++; c->stats.bytes[d0.coll] += (unsigned long long)d0.count * esz_real;
+        skip |= fault_now(c); c->call_index++;
+      }
+      if (skip) return PICCL_OK;
+      nvtxRangePushA("exchange_ll");
+      void* args[] = {&xa};
+      cudaError_t e;
+      if (n > 1) e = cudaLaunchCooperativeKernel((const void*)xf, dim3(n * xa.n_cta), dim3(kLLBlock), args, 0, stream);
+      else e = cudaLaunchKernel((const void*)xf, dim3(xa.n_cta), dim3(kLLBlock), args, 0, stream);
+      nvtxRangePop();
+      if (e != cudaSuccess) return fail(PICCL_CUDA_ERROR, "low-latency exchange launch failed: %s", cudaGetErrorString(e));
+      return PICCL_OK;
+    }
+  }
+
   // through the switch: all ranks of the communicator in this launch (one real rank, or every virtual rank of an emulated group)
   if (d0.algo == ALGO_NVLS || env().proto == 3) {
     bool can = (op == 0 || op == 2 || op == 3 || !reducing) && (n == 1 ? !nvls_emulated(c0) : nvls_emulated(c0) && n == c0->nranks);

@@ -39,6 +39,7 @@ static void load() {
   e.max_cta = env_int("PICCL_MAX_CTA", 64);
   e.ll_kb = env_int("PICCL_LL_KB", 1024);         // largest all-reduce taken by the low-latency kernel; 0 turns it off
   e.llf_kb = env_int("PICCL_LLF_KB", 64);        // largest message (any collective) on the low-latency executor; 0 turns it off
+  e.llx_kb = env_int("PICCL_LLX_KB", 64);        // largest block per rank of an all-gather / reduce-scatter taken by the one-exchange low-latency kernel
   e.tp_mb = env_int("PICCL_TP_MB", 0);           // heap space for the fused tensor-parallel kernels (0: none)
   e.tp_feeders = env_int("PICCL_TP_FEEDERS", 24); // CTAs that push the local shard in all-gather -> GEMM
   e.exec_defer = env_int("PICCL_EXEC_DEFER", 0);

@@ -6,7 +6,7 @@
 // (default -1), PICCL_BLOCK_SIZE (1024), PICCL_MAX_GRID_SIZE (1024),
 // PICCL_MIN_GRID_SIZE (1).  Additions that do not change those semantics: the
 // value AUTO, PICCL_TIMEOUT_MS, PICCL_SCRATCH_MB, PICCL_SLOT_KB, PICCL_NSLOT,
-// PICCL_MAX_CTA, PICCL_LL_KB, PICCL_LLF_KB, PICCL_TP_MB, PICCL_TP_FEEDERS, PICCL_LAUNCH, PICCL_PERSIST_IDLE_US, PICCL_PROTO, PICCL_EXEC_DEFER, PICCL_NVLS, PICCL_NVLS_CHUNK_KB, PICCL_NVLS_DEPTH, PICCL_NVLS_CTA, PICCL_NVLS_MIN_KB, PICCL_NVLS_AUTO_KB, PICCL_NVLS_GRAN, PICCL_NVLS_PROFILE, PICCL_NVLS_BULK, PICCL_NVLS_FENCE, PICCL_NVLS_SUB, PICCL_LOG, PICCL_TRACE, PICCL_FAULT, PICCL_TUNE_FILE, PICCL_DEBUG.
+// PICCL_MAX_CTA, PICCL_LL_KB, PICCL_LLF_KB, PICCL_LLX_KB, PICCL_TP_MB, PICCL_TP_FEEDERS, PICCL_LAUNCH, PICCL_PERSIST_IDLE_US, PICCL_PROTO, PICCL_EXEC_DEFER, PICCL_NVLS, PICCL_NVLS_CHUNK_KB, PICCL_NVLS_DEPTH, PICCL_NVLS_CTA, PICCL_NVLS_MIN_KB, PICCL_NVLS_AUTO_KB, PICCL_NVLS_GRAN, PICCL_NVLS_PROFILE, PICCL_NVLS_BULK, PICCL_NVLS_FENCE, PICCL_NVLS_SUB, PICCL_LOG, PICCL_TRACE, PICCL_FAULT, PICCL_TUNE_FILE, PICCL_DEBUG.
 #pragma once
 #include <string>
 #include "../include/piccl_sched.h"
@@ -18,7 +18,7 @@ struct Env {
   int k[COLL_COUNT];
   int block_size, max_grid, min_grid;          // reference knobs (now size the fused executor)
   bool block_size_set, max_grid_set, min_grid_set;
-  int timeout_ms, scratch_mb, slot_kb, nslot, max_cta, ll_kb, llf_kb, tp_mb, tp_feeders;
+  int timeout_ms, scratch_mb, slot_kb, nslot, max_cta, ll_kb, llf_kb, llx_kb, tp_mb, tp_feeders;
   int log_level, debug;
   int exec_defer;                                // PICCL_EXEC_DEFER=1: the FIFO executor publishes counters lazily (exec_impl.cuh)
   int proto;                                     // PICCL_PROTO: 0 auto, 1 ll, 2 simple, 3 nvls (see env.cc)

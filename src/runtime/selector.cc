@@ -5,6 +5,7 @@
 // exchange step with every rank (PRM, k = n) while the message is latency
 // bound, the bandwidth-optimal ring above that.  The reference has no
 // selector: the user picks through the environment (src/piccl.c:257-285).
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -50,14 +51,14 @@ Algo select_algo_n(int n, Coll coll, size_t bytes, int* k, bool window) {
   if (window && n >= 4) {
     const size_t lo = (size_t)env().nvls_auto_kb << 10;
     if (coll == COLL_ALLREDUCE && bytes > lo) { if (k) *k = -1; return ALGO_NVLS; }
-    if ((coll == COLL_ALLGATHER || coll == COLL_REDUCE_SCATTER) && bytes * (size_t)n > lo / 4 && bytes <= ((size_t)32 << 20)) { if (k) *k = -1; return ALGO_NVLS; }
+    if ((coll == COLL_ALLGATHER || coll == COLL_REDUCE_SCATTER) && bytes * (size_t)n > lo / 4 && bytes > ((size_t)env().llx_kb << 10) && bytes <= ((size_t)32 << 20)) { if (k) *k = -1; return ALGO_NVLS; }
   }
   // Built-in rule, from sweeps on 2, 4 and 8 B200 (fp32 and bf16 sum):
   //   all-reduce      <= 4 KiB one exchange with every rank (PRM, k = n: 8 us on 8 GPUs); up to 32 MiB (8 MiB on two
   //                   ranks) recursive doubling, whose few steps beat the ring's 2(n-1) (222 vs 154 GB/s at 16 MiB on 8
   //                   GPUs); above that the bandwidth-optimal ring (600 vs 290 GB/s at 256 MiB)
-  //   all-gather / reduce-scatter   one exchange with every rank while tiny, the ring otherwise (the ring was ahead of
-  //                   the recursive schedules from 1 KiB per rank upwards)
+  //   all-gather / reduce-scatter   one exchange with every rank while a rank's block is small (flag-in-data lines, one launch),
+  //                   the ring otherwise
   //   broadcast / reduce   the segment-pipelined chain at every size (8.5 us at 1 KiB, 581 GB/s at 256 MiB on 8 GPUs,
   //                   the trees 8.8 us and 225 GB/s)
   int kk = n < 8 ? n : 8;
@@ -67,7 +68,8 @@ Algo select_algo_n(int n, Coll coll, size_t bytes, int* k, bool window) {
       if (bytes <= ((size_t)(n <= 2 ? 8 : 32) << 20)) { if (k) *k = 2; return ALGO_PRD; }
       return ALGO_RING;
     case COLL_ALLGATHER: case COLL_REDUCE_SCATTER:
-      if (bytes <= (size_t)16 << 10) { if (k) *k = kk; return ALGO_PRM; }
+      // one exchange with every rank in the low-latency kernel while a rank's block is small (up to 8 ranks: the radix is the rank count)
+      if (bytes <= ((size_t)(n <= 8 ? std::max(16, env().llx_kb) : 16) << 10)) { if (k) *k = kk; return ALGO_PRM; }
       return ALGO_RING;
     default:
       return ALGO_RING;

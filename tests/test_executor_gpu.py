@@ -219,6 +219,56 @@ def test_low_latency_path_matches_fifo_path(groups):
                 assert torch.equal(outs[r], outs[0])
 
 
+@pytest.mark.parametrize("n", [2, 3, 8])
+def test_low_latency_exchange_kernels(groups, n):
+    """Small all-gather / reduce-scatter with a one-exchange schedule (DIRECT, PRM with radix = rank count) run the flag-in-data
+    kernels of ll_exchange.cu; mixed with low-latency all-reduces back to back, no synchronisation, they share slots and epochs."""
+    g = groups(n)
+    launches0 = g.stats().launches
+    for rep in range(3):
+        results = []
+        for dtype, op, count in [(torch.float32, "sum", 777), (torch.bfloat16, "avg", 4099), (torch.int32, "max", 1), (torch.float16, "min", 3000), (torch.float64, "prod", 17)]:
+            xs = _inputs(n, n * count, dtype, seed=50 + rep)
+            if op == "prod":
+                xs = [x * 0 + 1 + 0.01 * (r + 1) for r, x in enumerate(xs)]
+            outs = [torch.zeros(count, device="cuda", dtype=dtype) for _ in range(n)]
+            g.run("reduce_scatter", xs, outs, count, op=op, algo="DIRECT")
+            results.append(("rs", dtype, op, count, xs, outs))
+            ys = _inputs(n, count, dtype, seed=60 + rep)
+            gath = [torch.zeros(n * count, device="cuda", dtype=dtype) for _ in range(n)]
+            g.run("allgather", ys, gath, count, algo="PRM", k=8 if n == 8 else n)
+            results.append(("ag", dtype, op, count, ys, gath))
+            zs = _inputs(n, count, dtype, seed=70 + rep)
+            red = [torch.zeros_like(z) for z in zs]
+            g.run("allreduce", zs, red, count, op="sum", algo="PRD" if n != 3 else "RING")
+            results.append(("ar", dtype, "sum", count, zs, red))
+        _check_ok(g)
+        for kind, dtype, op, count, xs, outs in results:
+            if kind == "ag":
+                for r in range(n):
+                    assert torch.equal(outs[r], torch.cat(xs)), f"allgather {dtype} {count} rank {r}"
+            elif kind == "rs":
+                ref = _ref_reduce(xs, op)
+                for r in range(n):
+                    got = outs[r].double() if dtype in (torch.int32, torch.int64) else outs[r].float()
+                    assert torch.allclose(got, ref[r * count:(r + 1) * count].to(got.dtype), atol=_tol(dtype, n), rtol=2e-2), f"reduce_scatter {dtype} {op} {count} rank {r}"
+            else:
+                ref = _ref_reduce(xs, "sum")
+                got = outs[0].double() if dtype in (torch.int32, torch.int64) else outs[0].float()
+                assert torch.allclose(got, ref.to(got.dtype), atol=_tol(dtype, n) * 4, rtol=2e-2), f"allreduce {dtype} {count}"
+    # unaligned user buffers and an odd number of bytes per rank
+    base = [torch.arange(1, 1 + n * 1001 + 1, device="cuda", dtype=torch.uint8) + r for r in range(n)]
+    xs = [b[1:1002] for b in base]
+    outs_base = [torch.zeros(n * 1001 + 3, device="cuda", dtype=torch.uint8) for _ in range(n)]
+    outs = [o[3:] for o in outs_base]
+    g.run("allgather", xs, outs, 1001, algo="DIRECT")
+    _check_ok(g)
+    for r in range(n):
+        assert torch.equal(outs[r], torch.cat(xs))
+    # every call above was one launch
+    assert g.stats().launches - launches0 == 3 * 15 + 1
+
+
 def test_persistent_launcher_serves_and_leaves():
     # separate process: the launch mode is read from the environment when the library is loaded
     import os
