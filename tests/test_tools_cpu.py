@@ -76,6 +76,67 @@ def test_simulator_cli_and_stats(world, tmp_path):
     assert "finish_time" in (tmp_path / "o/stats.json").read_text()
 
 
+def test_contention_statistics_are_kept_per_group(world, tmp_path):
+    """Reference: sim.py:124-153 prints attempts / successes / largest queue per level-0 group.  Two transfers leave group 0
+    through its one NIC at the same time, a third stays inside group 1: group 0 shows one sender that had to wait."""
+    topo, sched = world
+    s, t = sched([(2, 0, 4, "-1"), (2, 1, 5, "-1"), (2, 6, 7, "-1")], "groups"), topo(2)
+    sim = S.Simulator(s, t, radix=1)
+    sim.run()
+    g0, g1 = sim.group_stats["0"], sim.group_stats["1"]
+    assert g0["send"] == {"attempts": 2, "success": 1, "waited": pytest.approx(20.0), "max_queue_size": 1}      # the NIC is busy for G s = 20
+    assert g1["send"]["attempts"] == 1 and g1["send"]["success"] == 1 and g1["send"]["max_queue_size"] == 0
+    assert g1["recv"]["attempts"] == 3 and g0["recv"]["attempts"] == 0
+    sim.output_stats(tmp_path / "stats.json")
+    assert '"groups"' in (tmp_path / "stats.json").read_text()
+    sim.output_stats(tmp_path / "report.txt")
+    rep = (tmp_path / "report.txt").read_text()
+    assert "Send Contention" in rep and "Group 0: 1 / 2 = 0.5 attempts successful" in rep and "Max Queue Size: 1" in rep
+
+
+def _chunked_nic_reference(sizes, G, mtu=4096):
+    """What the reference's chunk-level scheduler does with transfers that share one NIC and are ready at the same time
+    (schedulers/loggpc_scheduler.py:319-377): every transfer puts one chunk of at most `mtu` bytes into the NIC's FIFO, the NIC
+    serves the queue head for G * bytes, and the owner of a served chunk queues its next one.  Returns when each transfer's
+    last chunk has left the NIC."""
+    left = list(sizes)
+    queue = list(range(len(sizes)))
+    t, done = 0.0, [0.0] * len(sizes)
+    while queue:
+        i = queue.pop(0)
+        b = min(mtu, left[i])
+        t += G * b
+        left[i] -= b
+        if left[i] > 0:
+            queue.append(i)
+        else:
+            done[i] = t
+    return done
+
+
+def test_whole_message_nic_model_against_chunked_interleaving_for_large_transfers(world):
+    """Two 64 MiB transfers and a 16 MiB one leave a group through its single NIC at the same time.  The NIC is never idle in
+    either model, so the LAST transfer ends at the same time whether the NIC takes whole messages in order (this simulator) or
+    4096-byte chunks round robin (the reference); the earlier ones end later with chunks.  The makespan of a schedule whose
+    steps wait for all their transfers is therefore the same, which is what the fixtures above check on small messages."""
+    topo, sched = world
+    sizes = [64 << 20, 64 << 20, 16 << 20]
+    s, t = sched([(sizes[0], 0, 4, "-1"), (sizes[1], 1, 5, "-1"), (sizes[2], 2, 6, "-1")], "big"), topo(2)
+    sim = S.Simulator(s, t, radix=1)
+    sim.run()
+    G = 10.0
+    chunked = _chunked_nic_reference(sizes, G)
+    # time at which each transfer's bytes have left the source NIC in this simulator: it started o_s = 5 after time 0 and waited for the NIC
+    fixed = 5 + 100 + 6                                                   # o_s + L + o_r of the inter-group profile
+    left_nic = sorted(tk.done - fixed + G for tk in sim.tasks.values())   # done = nic start + G (s - 1) + L + o_r
+    assert left_nic[-1] - 5 == pytest.approx(max(chunked), rel=1e-6)      # the last one: same time, the NIC was busy throughout
+    assert left_nic[-1] - 5 == pytest.approx(G * sum(sizes), rel=1e-6)
+    # the earlier ones: whole messages in order let the first finish after its own bytes; with chunks the 16 MiB transfer shares
+    # the NIC three ways and needs almost three times its own bytes
+    assert left_nic[0] - 5 == pytest.approx(G * sizes[0], rel=1e-6)
+    assert min(chunked) > G * sizes[2] * 2.9
+
+
 def test_simulator_rejects_bad_schedules(world):
     topo, sched = world
     bad = sched([("1024.0", 0, 1, "-1")], "float_size")
@@ -260,6 +321,19 @@ def test_builtin_rule_and_tuning_table_of_the_library():
                                                            [4, "allreduce", 1024]])
     assert got[0] == ["PRM", 8] and got[1] == ["PRM", 2] and got[2] == ["PRM", 2] and got[3][0] == "RING"
     assert got[4] == ["PRM", 4]                                    # no row for 4 ranks in that table: the built-in rule
+    # with an NVLink multicast window (piccl_select_algorithm_ex): large all-reduces and mid-size all-gathers / reduce-scatters go
+    # through the switch from four ranks on; small ones, two ranks, broadcast and reduce do not
+    code = ("import ctypes as C, sys, json; sys.path.insert(0, %r); from piccl_b200 import _native as N; l = N.lib(); out = []\n"
+            "names = {v: k for k, v in N.ALGO.items()}\n"
+            "for n, coll, b in json.loads(sys.argv[1]):\n"
+            "    k = C.c_int(-9); a = l.piccl_select_algorithm_ex(n, N.COLL[coll], C.c_ulonglong(b), 1, C.byref(k)); out.append(names[a])\n"
+            "print(json.dumps(out))") % str(ROOT)
+    import json
+    import os
+    qs = [[8, "allreduce", 25 << 20], [8, "allreduce", 1 << 20], [2, "allreduce", 1 << 28], [4, "allreduce", 1 << 28], [8, "allgather", 1 << 20], [8, "allgather", 64 << 20],
+          [8, "allgather", 32 << 10], [8, "reduce_scatter", 4 << 20], [8, "broadcast", 1 << 28], [8, "reduce", 1 << 28]]
+    r = subprocess.run([sys.executable, "-c", code, json.dumps(qs)], env=dict(os.environ, PICCL_TUNE_FILE=""), capture_output=True, text=True, check=True)
+    assert json.loads(r.stdout.strip().splitlines()[-1]) == ["NVLS", "PRD", "RING", "NVLS", "NVLS", "RING", "PRM", "NVLS", "RING", "RING"]
 
 
 def test_profile_fitted_from_a_measured_ring_sweep_predicts_the_other_schedules(tmp_path):

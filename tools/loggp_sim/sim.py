@@ -23,7 +23,17 @@ Model.  A transfer of s bytes from a to b:
     the END of the previous send on the port, the receive gap from the START of the previous
     receive; a NIC is busy for G s.
 Large transfers cost the same closed form (no per-4-KiB events), so 1 GiB schedules simulate
-instantly.
+instantly.  A NIC serves whole messages in arrival order; the reference streams 4096-byte chunks
+through its NIC queues (schedulers/loggpc_scheduler.py:22,284-377), which interleaves messages that
+share a NIC: the LAST of them ends at the same time in both models (the NIC is never idle), the
+earlier ones end later there.  tests/test_tools_cpu.py compares the two on large transfers.
+
+Contention statistics (--output; reference: sim.py:124-153, loggpc_scheduler.py:272-291,411-428)
+are kept per level-0 group of the topology, for the send side (the group of the source) and the
+receive side (the group of the destination): attempts (one per transfer), success (started without
+waiting for a port or a NIC), the time waited, and the largest number of transfers that were
+waiting at the same time.  --output x.json writes them with the per-transfer times; any other
+name gets a text report in the layout of the reference's.
 """
 from __future__ import annotations
 
@@ -173,10 +183,35 @@ class Simulator:
         self.nic_s = {k: Ports(c) for k, c in self.topo.nics.items() if c}
         self.nic_r = {k: Ports(c) for k, c in self.topo.nics.items() if c}
         self.stats = {"send_wait": 0.0, "recv_wait": 0.0, "nic_wait": 0.0}
+        self.group_stats: dict = {}                     # level-0 group id -> {"send": {...}, "recv": {...}}
+        self._waits: dict = {}                          # (group id, side) -> [(asked, started)] of the transfers that waited
         for t in self.tasks.values():
             for n in (t.src, t.dst):
                 if n not in self.send:
                     raise ValueError(f"transfer {t.id} uses node {n}, which is not in the topology")
+
+    def _group_id(self, node) -> str:
+        k = self.topo.group0[node]
+        return str(k[1]) if len(k) > 1 else "flat"
+
+    def _note(self, node, side: str, asked: float, started: float) -> None:
+        gid = self._group_id(node)
+        st = self.group_stats.setdefault(gid, {x: {"attempts": 0, "success": 0, "waited": 0.0, "max_queue_size": 0} for x in ("send", "recv")})[side]
+        st["attempts"] += 1
+        if started <= asked:
+            st["success"] += 1
+        else:
+            st["waited"] += started - asked
+            self._waits.setdefault((gid, side), []).append((asked, started))
+
+    def _finish_group_stats(self) -> None:
+        for (gid, side), iv in self._waits.items():
+            ev = sorted([(a, 1) for a, _ in iv] + [(b, -1) for _, b in iv], key=lambda e: (e[0], e[1]))
+            cur = best = 0
+            for _, d in ev:
+                cur += d
+                best = max(best, cur)
+            self.group_stats[gid][side]["max_queue_size"] = best
 
     def prof(self, a, b) -> Profile:
         f = self.topo.pair_profile_file(a, b)
@@ -221,6 +256,7 @@ class Simulator:
                     st = ns
                     nic.free[ni] = st + G * s
                 self.stats["send_wait"] += st - now
+                self._note(task.src, "send", now, st)
                 ports = self.send[task.src]
                 ports.free[pi] = st + wire
                 ports.mark[pi] = st + wire if self.compat else st
@@ -237,12 +273,21 @@ class Simulator:
                     pi = min(range(len(rp.free)), key=lambda i: rp.free[i])
                     st = max(now, rp.free[pi] + max(g, G * s)) if rp.free[pi] > 0.0 else now
                 nic = self.nic_r.get(self.topo.group0[task.dst]) if inter else None
-                if nic is not None:
+                if nic is not None and self.compat:
                     ns, ni = nic.reserve(st, 0.0)
                     self.stats["nic_wait"] += ns - st
                     st = ns
                     nic.free[ni] = st + G * s
+                elif nic is not None:
+                    # classical: the destination NIC carries the message WHILE it arrives, from its first byte (st - wire) on,
+                    # not after its last byte; a message only waits if the NIC is still taking an earlier one
+                    first = st - wire
+                    ns, ni = nic.reserve(first, 0.0)
+                    self.stats["nic_wait"] += ns - first
+                    nic.free[ni] = ns + G * s
+                    st += ns - first
                 self.stats["recv_wait"] += st - now
+                self._note(task.dst, "recv", now, st)
                 ports = self.recv[task.dst]
                 busy = wire if self.compat else 0.0          # the classical model charges the bytes once
                 ports.free[pi] = st + busy
@@ -258,13 +303,33 @@ class Simulator:
                         post(now, 0, self.tasks[c])
         if finished != len(self.tasks):
             raise RuntimeError("Not all tasks completed (dependency cycle in the schedule?)")
+        self._finish_group_stats()
         return last
 
-    def output_stats(self, path) -> None:
-        out = {"finish_time": max((t.done for t in self.tasks.values()), default=0.0), **self.stats,
-               "tasks": {str(t.id): {"start": t.start, "done": t.done, "src": t.src, "dst": t.dst, "size": t.size} for t in self.tasks.values()}}
+    def output_stats(self, path, args=None) -> None:
+        finish = max((t.done for t in self.tasks.values()), default=0.0)
         Path(path).parent.mkdir(parents=True, exist_ok=True)
-        Path(path).write_text(json.dumps(out, indent=1))
+        if str(path).endswith(".json"):
+            out = {"finish_time": finish, **self.stats, "groups": self.group_stats,
+                   "tasks": {str(t.id): {"start": t.start, "done": t.done, "src": t.src, "dst": t.dst, "size": t.size} for t in self.tasks.values()}}
+            Path(path).write_text(json.dumps(out, indent=1))
+            return
+        # the text report of the reference's simulator (same headings), per level-0 group
+        lines = ["LogGP Simulation Output", "", "====================================", "", "Simulation args:"]
+        if args is not None:
+            lines += [f"  Schedule: {args.schedule}", f"  Topology: {args.topo}", f"  Device radix: {args.radix}", f"  Output file: {args.output}"]
+        lines += ["", "====================================", "", "Simulation Overview:", f"  Simulation finished at time {finish * 1e6} us",
+                  f"  Number of tasks: {len(self.tasks)}", f"  Number of completed tasks: {sum(1 for t in self.tasks.values() if t.done >= 0)}",
+                  "", "====================================", "", "Scheduler Statistics:"]
+        for side, title in (("send", "Send Contention"), ("recv", "Recv Contention")):
+            lines.append(f"  {title}: ")
+            for gid in sorted(self.group_stats):
+                st = self.group_stats[gid][side]
+                if st["attempts"]:
+                    lines.append(f"    Group {gid}: {st['success']} / {st['attempts']} = {st['success'] / st['attempts']} attempts successful")
+                    lines.append(f"    Max Queue Size: {st['max_queue_size']}")
+                    lines.append(f"    Time waited: {st['waited'] * 1e6} us")
+        Path(path).write_text("\n".join(lines) + "\n")
 
 
 def simulate(schedule, topo, radix=1, compat=False, gamma=0.0, alpha=0.0) -> float:
@@ -285,7 +350,7 @@ def main(argv=None) -> int:
     sim = Simulator(a.schedule, a.topo, a.radix, a.compat, a.gamma, a.alpha)
     t = sim.run()
     if a.output:
-        sim.output_stats(a.output)
+        sim.output_stats(a.output, a)
     print(t * 1e6)
     return 0
 
