@@ -328,6 +328,22 @@ static int get_program(piccl_comm* c, const CollArgs& a, cudaStream_t stream, co
   ProgKey k{(int)a.coll, (int)a.algo, a.k, a.root, a.elem_size, a.in_place ? 1 : 0, a.count, a.block_stride};
   auto it = c->cache.find(k);
   if (it == c->cache.end()) {
+    // A new program needs device and pinned memory and an upload on the caller's stream: not inside a stream capture (an
+    // allocation ends a capture in the global mode, and the upload's event would belong to the graph).  The caller runs
+    // the call once before capturing, or, in the preload library, the call goes to NCCL.
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cs) == cudaSuccess && cs != cudaStreamCaptureStatusNone) {
+      c->stats.fallbacks++;
+      return fail(PICCL_UNSUPPORTED, "%s %s of %lld elements was never run outside a stream capture: its program cannot be built while capturing", coll_name(a.coll), algo_name(a.algo), a.count);
+    }
+    cudaGetLastError();
+    // programs are kept for the life of the communicator (kernels in flight may read them): bound what they may take
+    size_t held = 0;
+    for (const auto& ch : c->chunks) held += ch.cap;
+    if (held > ((size_t)256 << 20)) {
+      c->stats.fallbacks++;
+      return fail(PICCL_UNSUPPORTED, "program cache full (%zu MiB for %zu distinct calls)", held >> 20, c->cache.size());
+    }
     c->stats.program_cache_misses++;
     Program p = compile(a, c->rank);
     if (env().debug) {
