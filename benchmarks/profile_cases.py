@@ -11,6 +11,7 @@
     python benchmarks/profile_cases.py nvls      # in-switch all-reduce kernel with the switch emulated: 4 virtual ranks, 64 MiB bf16 each
     python benchmarks/profile_cases.py llf       # low-latency executor: all-gather of 16 KiB per rank, 8 virtual ranks
     python benchmarks/profile_cases.py ag_gemm   # fused all-gather -> GEMM, 2 virtual ranks, 4096 x 2048 x 4096
+    python benchmarks/profile_cases.py elementwise  # AdamW on 128 Mi parameters, bias + GELU forward / backward on 8192 x 4096, embedding 8192 x 1024, column sum
 
 Typical capture (after the same command has exited 0 without ncu):
     ncu --set full --clock-control none -k regex:<kernel> -s 2 -c 2 -o <name> python benchmarks/profile_cases.py <case>
@@ -135,6 +136,30 @@ def case_ag_gemm():
     g.close()
 
 
+def case_elementwise():
+    """The memory-bound model kernels of src/ops/elementwise.cu on GPT-2-medium shapes (operands far larger than L2)."""
+    from piccl_b200 import ops
+    n = 128 << 20
+    p = torch.zeros(n, device="cuda", dtype=torch.bfloat16); master = torch.zeros(n, device="cuda")
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    g = torch.full((n,), 0.01, device="cuda", dtype=torch.bfloat16)
+    T, H, C_ = 8192, 4096, 1024
+    h = torch.randn(T, H, device="cuda").bfloat16(); bias = torch.randn(H, device="cuda").bfloat16()
+    h_out, act, dh = torch.empty_like(h), torch.empty_like(h), torch.empty_like(h)
+    idx = torch.randint(0, 50257, (T,), device="cuda")
+    wte = torch.randn(50304, C_, device="cuda").bfloat16(); wpe = torch.randn(1024, C_, device="cuda").bfloat16()
+    emb = torch.empty(T, C_, device="cuda", dtype=torch.bfloat16)
+    cs = torch.empty(H, device="cuda", dtype=torch.bfloat16)
+    for step in range(1, 3):
+        ops.adamw(p, master, m, v, g, 3e-4, 0.9, 0.95, 1e-8, 0.1, step)
+        ops.bias_gelu_fwd(h, bias, h_out, act)
+        ops.gelu_bwd(act, h_out, dh)
+        ops.embed_fwd(idx, wte, wpe, emb, 1024)
+        ops.colsum(dh, cs)
+    torch.cuda.synchronize()
+    assert torch.isfinite(cs.float()).all() and float(master.abs().max()) > 0
+
+
 def case_ln():
     from piccl_b200 import ops
     T, C = 8192 * 4, 1024
@@ -162,5 +187,5 @@ def case_ce():
 
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "exec"
-    {"exec": case_exec, "exec_ll": lambda: case_exec(True), "gemm": case_gemm, "gemm_pair": case_gemm_pair, "direct": case_direct, "tp": case_tp, "ln": case_ln, "ce": case_ce, "nvls": case_nvls, "llf": case_llf, "ag_gemm": case_ag_gemm}[which]()
+    {"exec": case_exec, "exec_ll": lambda: case_exec(True), "gemm": case_gemm, "gemm_pair": case_gemm_pair, "direct": case_direct, "tp": case_tp, "ln": case_ln, "ce": case_ce, "nvls": case_nvls, "llf": case_llf, "ag_gemm": case_ag_gemm, "elementwise": case_elementwise}[which]()
     print(f"profile case {which} done")
