@@ -319,7 +319,7 @@ def test_builtin_rule_and_tuning_table_of_the_library():
     table = ROOT / "tools" / "selector" / "tables" / "b200_8gpu.csv"
     got = _select_in_child({"PICCL_TUNE_FILE": str(table)}, [[8, "allreduce", 1024], [8, "allreduce", 32768], [8, "allreduce", 2 << 20], [8, "allreduce", 1 << 30],
                                                            [4, "allreduce", 1024]])
-    assert got[0] == ["PRM", 8] and got[1] == ["PRM", 2] and got[2] == ["PRM", 2] and got[3][0] == "RING"
+    assert got[0] == ["PRM", 8] and got[1] == ["PRM", 2] and got[2] == ["PRD", -1] and got[3][0] == "RING"     # no window: the in-switch rows are skipped
     assert got[4] == ["PRM", 4]                                    # no row for 4 ranks in that table: the built-in rule
     # with an NVLink multicast window (piccl_select_algorithm_ex): large all-reduces and mid-size all-gathers / reduce-scatters go
     # through the switch from four ranks on; small ones, two ranks, broadcast and reduce do not
@@ -334,6 +334,9 @@ def test_builtin_rule_and_tuning_table_of_the_library():
           [8, "allgather", 32 << 10], [8, "reduce_scatter", 4 << 20], [8, "broadcast", 1 << 28], [8, "reduce", 1 << 28]]
     r = subprocess.run([sys.executable, "-c", code, json.dumps(qs)], env=dict(os.environ, PICCL_TUNE_FILE=""), capture_output=True, text=True, check=True)
     assert json.loads(r.stdout.strip().splitlines()[-1]) == ["NVLS", "PRD", "RING", "NVLS", "NVLS", "RING", "PRM", "NVLS", "RING", "RING"]
+    # the same questions answered from the 8-GPU table: its in-switch rows apply when there is a window
+    r = subprocess.run([sys.executable, "-c", code, json.dumps([q for q in qs if q[0] == 8])], env=dict(os.environ, PICCL_TUNE_FILE=str(table)), capture_output=True, text=True, check=True)
+    assert json.loads(r.stdout.strip().splitlines()[-1]) == ["NVLS", "PRD", "NVLS", "RING", "PRM", "NVLS", "RING", "RING"]
 
 
 def test_profile_fitted_from_a_measured_ring_sweep_predicts_the_other_schedules(tmp_path):

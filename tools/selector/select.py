@@ -7,7 +7,9 @@ Two sources:
   --profile P.csv     predict every candidate with the LogGP simulator (tools/loggp_sim) on a flat
                       topology whose links use the fitted profile P (from tools/loggp_param)
   --from-bench F.csv  take the fastest measured candidate per size from coll_bench output
-                      (label column `ours-<ALGO>-k<K>`)
+                      (label column `ours-<ALGO>-k<K>`; --alias LABEL=ALGO:K[:MAX_BYTES] names what a run with
+                      another label measured, e.g. nvls=NVLS:-1, or ours-AUTO-k-1=PRM:8:65536 for the sizes at
+                      which AUTO is known to have run that algorithm)
 The reference has no selector; its user sets PICCL_<COLL>_ALGO by hand (README.md:46-68).
 """
 from __future__ import annotations
@@ -83,20 +85,27 @@ def table_from_profile(profile: str, ranks, min_b: int, max_b: int, gamma: float
     return rows
 
 
-def table_from_bench(paths):
+def table_from_bench(paths, aliases=None):
+    aliases = aliases or {}
     best: dict = {}
     for p in paths:
         with open(p) as f:
             for r in csv.reader(f):
-                if len(r) < 9 or r[0].startswith("#"):
+                if len(r) < 9 or r[0].startswith("#") or (len(r) > 10 and r[10] == "FAIL"):
                     continue
-                m = re.match(r"ours-([A-Z_]+)-k(-?\d+)", r[1])
-                if not m or (len(r) > 10 and r[10] == "FAIL"):
-                    continue
+                if r[1] in aliases:
+                    algo, k, max_b = aliases[r[1]]
+                    if max_b is not None and int(r[5]) > max_b:
+                        continue
+                else:
+                    m = re.match(r"ours-([A-Z_]+)-k(-?\d+)", r[1])
+                    if not m or m.group(1) == "AUTO":
+                        continue
+                    algo, k = m.group(1), int(m.group(2))
                 key = (r[0], int(r[4]), int(r[5]))
                 t = float(r[7])
                 if key not in best or t < best[key][0]:
-                    best[key] = (t, m.group(1), int(m.group(2)))
+                    best[key] = (t, algo, k)
     rows = []
     for coll, n in sorted({(c, n) for c, n, _ in best}):
         per = [(b, best[(coll, n, b)][1], best[(coll, n, b)][2]) for b in sorted(b for c, m, b in best if c == coll and m == n)]
@@ -108,6 +117,7 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description="Build the algorithm selection table")
     ap.add_argument("--profile", help="fitted LogGP CSV (s,L,o_s,o_r,g,G)")
     ap.add_argument("--from-bench", nargs="*", help="coll_bench CSV files with ours-<ALGO>-k<K> labels")
+    ap.add_argument("--alias", action="append", default=[], help="LABEL=ALGO:K[:MAX_BYTES]: rows with this label measured that algorithm (up to that size)")
     ap.add_argument("--ranks", default="2,4,8")
     ap.add_argument("--min", type=int, default=8)
     ap.add_argument("--max", type=int, default=1 << 30)
@@ -115,7 +125,12 @@ def main(argv=None) -> int:
     ap.add_argument("--output", required=True)
     a = ap.parse_args(argv)
     if a.from_bench:
-        rows = table_from_bench(a.from_bench)
+        aliases = {}
+        for spec in a.alias:
+            label, what = spec.split("=", 1)
+            parts = what.split(":")
+            aliases[label] = (parts[0], int(parts[1]) if len(parts) > 1 else -1, int(parts[2]) if len(parts) > 2 else None)
+        rows = table_from_bench(a.from_bench, aliases)
     elif a.profile:
         rows = table_from_profile(a.profile, [int(x) for x in a.ranks.split(",")], a.min, a.max, a.gamma)
     else:
