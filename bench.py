@@ -169,7 +169,7 @@ def run_collectives(world: int):
     ref_missing = ensure_reference()
     ref = str(reference_paths())
     sizes = ",".join(str(b) for b in COLL_SIZES)
-    table = {"sizes_bytes": COLL_SIZES, "iters": "1000 below 1 MB, 100 from 1 MB", "unit": "us per call, max over ranks", "failed_checks": 0}
+    table = {"sizes_bytes": COLL_SIZES, "iters": "1000 below 1 MB, 100 from 1 MB", "unit": "us per call, max over ranks", "failed_checks": {"ours": 0, "nccl": 0, "ref": 0}}
 
     def bench(dtype, label, preload, env_extra, algos=None):
         cmd = [str(cb), "--gpus", str(world), "--coll", "allreduce", "--dtype", dtype, "--sizes", sizes, "--check", "--label", label]
@@ -188,7 +188,7 @@ def run_collectives(world: int):
             if len(f) == 11 and f[0] == "allreduce":
                 rows.setdefault(f[1], {})[int(f[5])] = round(float(f[7]), 1)
                 if f[10] == "FAIL":
-                    table["failed_checks"] += 1
+                    table["failed_checks"][f[1].split("-")[0] if f[1].split("-")[0] in ("ours", "nccl", "ref") else "ours"] += 1
         if not rows:
             return {label: f"no rows (rc {r.returncode})"}
         return {k: [v.get(b) for b in COLL_SIZES] for k, v in rows.items()}
