@@ -213,6 +213,17 @@ def test_selector_tables(tmp_path):
     assert select.main(["--from-bench", str(bench), "--output", str(out)]) == 0
     rows = [l.split(",") for l in out.read_text().splitlines() if not l.startswith("#")]
     assert rows[0][:5] == ["allreduce", "8", "8", "PRM", "8"] and rows[1][3] == "RING"
+    # the in-switch path enters the model-driven table through a fit of its measured times: T = 30 us + bytes / 400 GB/s here
+    nv = tmp_path / "nv.csv"
+    nv.write_text("".join(f"allreduce,sw,float,sum,8,{b},10,{30.0 + b / 400e3:.3f},0,0,ok\n" for b in (1 << 20, 1 << 24, 1 << 28)))
+    fit = select.fit_nvls([str(nv)], {"sw": ("NVLS", -1, None)})
+    assert fit[("allreduce", 8)][0] == pytest.approx(30e-6, rel=1e-3) and fit[("allreduce", 8)][1] == pytest.approx(400e9, rel=1e-3)
+    assert select.main(["--profile", str(prof), "--ranks", "8", "--min", "8", "--max", str(1 << 28), "--nvls-bench", str(nv), "--alias", "sw=NVLS:-1",
+                        "--output", str(out)]) == 0
+    rows = [l.split(",") for l in out.read_text().splitlines() if not l.startswith("#")]
+    ar = [r for r in rows if r[0] == "allreduce"]
+    assert ar[0][3] != "NVLS" and ar[-1][3] == "NVLS"             # 100 GB/s links in the profile: the switch wins the large sizes
+    assert all(r[3] != "NVLS" for r in rows if r[0] != "allreduce")
 
 
 # ---------------------------------------------------------------- per-rank lists and the matcher

@@ -10,6 +10,10 @@ Two sources:
                       (label column `ours-<ALGO>-k<K>`; --alias LABEL=ALGO:K[:MAX_BYTES] names what a run with
                       another label measured, e.g. nvls=NVLS:-1, or ours-AUTO-k-1=PRM:8:65536 for the sizes at
                       which AUTO is known to have run that algorithm)
+With --profile, --nvls-bench F.csv adds the in-switch path as a candidate.  It is not a schedule of point-to-point transfers, so
+the LogGP simulator cannot replay it; its cost is fitted from measurements instead: T(bytes) = a + bytes / B per collective and rank
+count (least squares over the rows of F whose label, after --alias, names NVLS), a = the fill / switch / out pipeline's start-up,
+B = its steady-state rate.
 The reference has no selector; its user sets PICCL_<COLL>_ALGO by hand (README.md:46-68).
 """
 from __future__ import annotations
@@ -66,14 +70,41 @@ def compress(rows):
     return out
 
 
-def table_from_profile(profile: str, ranks, min_b: int, max_b: int, gamma: float):
+def fit_nvls(paths, aliases):
+    """(collective, ranks) -> (a seconds, B bytes per second) of T = a + bytes / B, from coll_bench rows that measured NVLS."""
+    import numpy as np
+    pts: dict = {}
+    for p in paths:
+        with open(p) as f:
+            for r in csv.reader(f):
+                if len(r) < 9 or r[0].startswith("#") or (len(r) > 10 and r[10] == "FAIL"):
+                    continue
+                algo = aliases[r[1]][0] if r[1] in aliases else (re.match(r"ours-([A-Z_]+)-k", r[1]) or [None, None])[1]
+                if algo == "NVLS":
+                    pts.setdefault((r[0], int(r[4])), []).append((int(r[5]), float(r[7]) * 1e-6))
+    out = {}
+    for key, v in pts.items():
+        if len(v) < 2:
+            continue
+        b, t = np.array(sorted(v)).T
+        slope, a = np.polyfit(b, t, 1, w=1.0 / t)               # relative errors: the small sizes pin a, the large ones B
+        if slope > 0:
+            out[key] = (max(float(a), 0.0), 1.0 / float(slope))
+    return out
+
+
+def table_from_profile(profile: str, ranks, min_b: int, max_b: int, gamma: float, nvls=None):
     rows = []
+    nvls = nvls or {}
     for coll in COLLS:
         for n in ranks:
             per = []
             b = min_b
             while b <= max_b:
                 best = None
+                if (coll, n) in nvls:
+                    a_, B_ = nvls[(coll, n)]
+                    best = (a_ + b / B_, "NVLS", -1)
                 for algo, k in candidates(n):
                     # small messages: injections overlap (radix n); large: the egress link is shared (one port)
                     t = predict(profile, coll, n, b, algo, k, radix=n if b <= 16384 else 1, gamma=gamma)
@@ -122,17 +153,22 @@ def main(argv=None) -> int:
     ap.add_argument("--min", type=int, default=8)
     ap.add_argument("--max", type=int, default=1 << 30)
     ap.add_argument("--gamma", type=float, default=0.0, help="reduction cost per byte (s/B)")
+    ap.add_argument("--nvls-bench", nargs="*", default=[], help="with --profile: coll_bench CSV files with rows that measured the in-switch path (label ours-NVLS-k-1 or an --alias)")
     ap.add_argument("--output", required=True)
     a = ap.parse_args(argv)
+    aliases = {}
+    for spec in a.alias:
+        label, what = spec.split("=", 1)
+        parts = what.split(":")
+        aliases[label] = (parts[0], int(parts[1]) if len(parts) > 1 else -1, int(parts[2]) if len(parts) > 2 else None)
     if a.from_bench:
-        aliases = {}
-        for spec in a.alias:
-            label, what = spec.split("=", 1)
-            parts = what.split(":")
-            aliases[label] = (parts[0], int(parts[1]) if len(parts) > 1 else -1, int(parts[2]) if len(parts) > 2 else None)
         rows = table_from_bench(a.from_bench, aliases)
     elif a.profile:
-        rows = table_from_profile(a.profile, [int(x) for x in a.ranks.split(",")], a.min, a.max, a.gamma)
+        nvls = fit_nvls(a.nvls_bench, aliases) if a.nvls_bench else None
+        if nvls:
+            for (coll, n), (a_, B_) in sorted(nvls.items()):
+                print(f"in-switch {coll} on {n} ranks: T = {a_ * 1e6:.1f} us + bytes / {B_ / 1e9:.0f} GB/s")
+        rows = table_from_profile(a.profile, [int(x) for x in a.ranks.split(",")], a.min, a.max, a.gamma, nvls)
     else:
         ap.error("give --profile or --from-bench")
     with open(a.output, "w") as f:
